@@ -1,0 +1,184 @@
+"""ctypes binding of the C ABI declared in include/chill_b200.h.
+
+The shared library is built in-tree (``python chill-attention_b200/build.py``) as
+``chill_attention/_lib/libchill_b200.so``.  There is no other implementation behind
+this module: if the library is missing, or a call returns a non-zero status, the
+caller gets an exception.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_DIR = os.path.join(_HERE, "_lib")
+DEFAULT_LIB = os.path.join(LIB_DIR, "libchill_b200.so")
+
+CHILL_F32, CHILL_F16, CHILL_BF16 = 0, 1, 2
+MASK_FULL, MASK_CAUSAL, MASK_SLIDING, MASK_CHUNKWISE, MASK_PREFIXLM, MASK_CUSTOM = range(6)
+FLAG_FORCE_GENERIC, FLAG_REQUIRE_TC = 1, 2
+MAX_MASK_ARGS = 8
+
+BUILTIN_FUNCTOR_IDS = {
+    "FullMask": MASK_FULL,
+    "CausalMask": MASK_CAUSAL,
+    "SlidingWindowMask": MASK_SLIDING,
+    "ChunkwiseMask": MASK_CHUNKWISE,
+    "PrefixLMMask": MASK_PREFIXLM,
+}
+
+_DTYPES = {torch.float32: CHILL_F32, torch.float16: CHILL_F16, torch.bfloat16: CHILL_BF16}
+
+EXPORTS = (
+    "chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_scratch_bytes", "chill_fwd_uses_tensor_cores",
+    "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits", "chill_read_device_status",
+    "chill_abi_version", "chill_status_string", "chill_last_cuda_error",
+)
+
+
+class MaskDesc(C.Structure):
+    _fields_ = [("id", C.c_int32), ("n_args", C.c_int32), ("i", C.c_int64 * MAX_MASK_ARGS),
+                ("f", C.c_double * MAX_MASK_ARGS)]
+
+
+class Shape(C.Structure):
+    _fields_ = [("B", C.c_int32), ("H", C.c_int32), ("H_kv", C.c_int32), ("Lq", C.c_int32), ("Lk", C.c_int32),
+                ("D", C.c_int32), ("dtype", C.c_int32), ("q_offset", C.c_int32), ("k_offset", C.c_int32),
+                ("seq_len", C.c_int32), ("sm_scale", C.c_float), ("flags", C.c_uint32), ("lens", C.c_void_p),
+                ("mask", MaskDesc)]
+
+
+_S4 = C.c_int64 * 4
+_S3 = C.c_int64 * 3
+
+
+class FwdArgs(C.Structure):
+    _fields_ = [("s", Shape), ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
+                ("lse", C.c_void_p), ("q_strides", _S4), ("k_strides", _S4), ("v_strides", _S4), ("o_strides", _S4),
+                ("lse_strides", _S3)]
+
+
+class BwdArgs(C.Structure):
+    _fields_ = [("s", Shape), ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
+                ("d_o", C.c_void_p), ("lse", C.c_void_p), ("delta", C.c_void_p), ("dq", C.c_void_p),
+                ("dk", C.c_void_p), ("dv", C.c_void_p), ("q_strides", _S4), ("k_strides", _S4), ("v_strides", _S4),
+                ("o_strides", _S4), ("do_strides", _S4), ("dq_strides", _S4), ("dk_strides", _S4),
+                ("dv_strides", _S4), ("lse_strides", _S3)]
+
+
+class ChillLibraryError(RuntimeError):
+    pass
+
+
+_libs: dict[str, C.CDLL] = {}
+_lock = threading.Lock()
+
+
+def load_library(path: str | None = None) -> C.CDLL:
+    """dlopen the kernel library (cached per path) and declare its prototypes."""
+    path = os.path.abspath(path or os.environ.get("CHILL_B200_LIB", DEFAULT_LIB))
+    with _lock:
+        lib = _libs.get(path)
+        if lib is not None:
+            return lib
+        if not os.path.exists(path):
+            raise ChillLibraryError(
+                f"{path} not found: build the CUDA library first (python chill-attention_b200/build.py). "
+                "chill_attention has no other backend."
+            )
+        lib = C.CDLL(path)
+        lib.chill_fwd.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
+        lib.chill_bwd_delta.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
+        lib.chill_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
+        lib.chill_bwd_scratch_bytes.argtypes = [C.POINTER(Shape)]
+        lib.chill_bwd_scratch_bytes.restype = C.c_size_t
+        lib.chill_fwd_uses_tensor_cores.argtypes = [C.POINTER(FwdArgs)]
+        lib.chill_bwd_uses_tensor_cores.argtypes = [C.POINTER(BwdArgs)]
+        lib.chill_mask_tabulate.argtypes = [C.POINTER(MaskDesc), C.c_int32, C.c_int32] + [C.c_void_p] * 6
+        lib.chill_mask_traits.argtypes = [C.c_int32]
+        lib.chill_status_string.argtypes = [C.c_int]
+        lib.chill_status_string.restype = C.c_char_p
+        lib.chill_last_cuda_error.restype = C.c_char_p
+        for name in ("chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_fwd_uses_tensor_cores",
+                     "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits",
+                     "chill_read_device_status", "chill_abi_version"):
+            getattr(lib, name).restype = C.c_int
+        if lib.chill_abi_version() != 1:
+            raise ChillLibraryError(f"{path}: ABI version {lib.chill_abi_version()} != 1")
+        _libs[path] = lib
+        return lib
+
+
+def check(lib, status: int, what: str):
+    if status != 0:
+        msg = lib.chill_status_string(status).decode()
+        extra = lib.chill_last_cuda_error().decode() if status == -3 else ""
+        raise ChillLibraryError(f"{what} failed: {msg} (status {status}) {extra}".strip())
+
+
+def mask_desc(mask_id: int, args) -> MaskDesc:
+    d = MaskDesc()
+    d.id = mask_id
+    args = tuple(args)
+    if len(args) > MAX_MASK_ARGS:
+        raise ValueError(f"a mask takes at most {MAX_MASK_ARGS} constants")
+    d.n_args = len(args)
+    for n, a in enumerate(args):
+        d.i[n] = int(a)
+        d.f[n] = float(a)
+    return d
+
+
+def make_shape(q, k, mask_id, mask_args, lens, sm_scale, q_offset=0, k_offset=0, seq_len=None, flags=0) -> Shape:
+    s = Shape()
+    s.B, s.H, s.Lq, s.D = q.shape
+    s.H_kv, s.Lk = k.shape[1], k.shape[2]
+    s.dtype = _DTYPES[q.dtype]
+    s.q_offset, s.k_offset = q_offset, k_offset
+    s.seq_len = s.Lq if seq_len is None else seq_len
+    s.sm_scale = sm_scale
+    s.flags = flags
+    s.lens = lens.data_ptr() if lens is not None else None
+    s.mask = mask_desc(mask_id, mask_args)
+    return s
+
+
+def _strides(t, n):
+    return (C.c_int64 * n)(*t.stride())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def forward(lib, q, k, v, o, lse, shape: Shape):
+    a = FwdArgs()
+    a.s = shape
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.q_strides, a.k_strides, a.v_strides, a.o_strides = (_strides(t, 4) for t in (q, k, v, o))
+    if lse is not None:
+        a.lse_strides = _strides(lse, 3)
+    check(lib, lib.chill_fwd(C.byref(a), _stream()), "chill_fwd")
+
+
+def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape) -> BwdArgs:
+    a = BwdArgs()
+    a.s = shape
+    a.q, a.k, a.v, a.o, a.d_o = (t.data_ptr() for t in (q, k, v, o, do))
+    a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    (a.q_strides, a.k_strides, a.v_strides, a.o_strides, a.do_strides, a.dq_strides, a.dk_strides,
+     a.dv_strides) = (_strides(t, 4) for t in (q, k, v, o, do, dq, dk, dv))
+    a.lse_strides = _strides(lse, 3)
+    return a
+
+
+def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape):
+    a = backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape)
+    st = _stream()
+    check(lib, lib.chill_bwd_delta(C.byref(a), st), "chill_bwd_delta")
+    check(lib, lib.chill_bwd(C.byref(a), st), "chill_bwd")

@@ -1,0 +1,234 @@
+"""Public API: ``chill_attention`` and ``register_chill_mask``.
+
+Same call surface as the reference (chill_attention/chill.py:579-645 and :30-495):
+one pair of dispatcher ops per mask CLASS NAME,
+
+    chill_attention::forward<Name>(q, k, v, lens, mask_args, sm_scale, return_lse,
+                                   prescale_qk, precision, autotune) -> (O, LSE)
+    chill_attention::backward<Name>(q, k, v, lens, o, lse, do, mask_args, sm_scale,
+                                    prescale_qk, precision, autotune) -> (dQ, dK, dV)
+
+registered as ``torch.library.custom_op`` with fake (meta) implementations and an
+autograd rule, so the call is opaque to and safe under ``torch.compile``.  The op
+bodies hand raw device pointers to the C ABI (include/chill_b200.h); kernels run on
+the current CUDA stream.  ``autotune`` and ``prescale_qk`` are accepted for
+compatibility and have no effect: there is nothing to tune at run time and the
+softmax scale is always applied in fp32 inside the exponent.
+``precision`` only matters for fp32 inputs, which are computed with IEEE fp32 FMAs.
+"""
+from __future__ import annotations
+
+import logging
+import typing
+
+import torch
+
+from . import _cabi
+from .mask import ChillMask
+
+logger = logging.getLogger(__name__)
+
+_HEAD_DIMS = {16, 32, 64, 128, 256}
+#: mask class name -> (library, functor id); filled by register_chill_mask
+_REGISTRY: dict[str, tuple] = {}
+
+
+def _resolve_functor(mask: ChillMask):
+    """Library + functor id serving this mask class (builds a custom library if needed)."""
+    functor = getattr(mask, "cuda_functor", None)
+    header = getattr(mask, "cuda_functor_header", None)
+    if header is not None:
+        from .custom import build_custom_library
+
+        if not functor:
+            raise ValueError(f"{mask.name}: cuda_functor_header is set but cuda_functor (struct name) is not")
+        return _cabi.load_library(build_custom_library(header, functor)), _cabi.MASK_CUSTOM
+    if functor in _cabi.BUILTIN_FUNCTOR_IDS:
+        return _cabi.load_library(), _cabi.BUILTIN_FUNCTOR_IDS[functor]
+    raise NotImplementedError(
+        f"{mask.name} has no CUDA functor: set `cuda_functor` to a built-in functor name or provide "
+        "`cuda_functor_header` + `cuda_functor` (see chill_attention/custom.py)"
+    )
+
+
+def _check_inputs(q, k, v, lens, sm_scale):
+    batch, heads, T, D = q.shape
+    assert heads % k.shape[1] == 0
+    assert D in _HEAD_DIMS
+    assert D == k.shape[-1] and D == v.shape[-1]
+    assert T == k.shape[-2] and T == v.shape[-2]
+    assert k.shape[1] == v.shape[1] and k.shape[0] == batch and v.shape[0] == batch
+    assert q.dtype == k.dtype == v.dtype and q.dtype in (torch.float32, torch.float16, torch.bfloat16)
+    assert sm_scale is not None
+    assert lens is None or (lens.dtype == torch.int32 and batch == len(lens) and lens.ndim == 1)
+    assert q.is_cuda and k.is_cuda and v.is_cuda, "chill_attention runs on CUDA tensors only"
+
+
+def register_chill_mask(mask: ChillMask):
+    """Create and register the forward/backward ops of ``type(mask)`` (idempotent per class name)."""
+    mask_name = mask.name
+    if hasattr(torch.ops.chill_attention, f"forward{mask_name}"):
+        return
+    lib, functor_id = _resolve_functor(mask)
+    _REGISTRY[mask_name] = (lib, functor_id)
+
+    @torch.library.custom_op(f"chill_attention::forward{mask_name}", mutates_args=(), device_types=("cuda",))
+    def attention_forward_adapter(
+        q: torch.Tensor,
+        k: torch.Tensor,
+        v: torch.Tensor,
+        lens: typing.Optional[torch.Tensor],
+        mask_args: typing.List[typing.Union[int, float, bool]],
+        sm_scale: float,
+        return_lse: bool,
+        prescale_qk: bool,
+        precision: str,
+        autotune: bool,
+    ) -> tuple[torch.Tensor, torch.Tensor]:
+        _check_inputs(q, k, v, lens, sm_scale)
+        with torch.cuda.device(q.device):
+            O = torch.empty_like(q, memory_format=torch.contiguous_format)
+            LSE = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if return_lse else None
+            lens_c = lens.contiguous() if lens is not None else None
+            shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale)
+            _cabi.forward(lib, q, k, v, O, LSE, shape)
+        if LSE is None:
+            LSE = torch.empty(0, dtype=torch.float32, device=q.device)
+        return O, LSE
+
+    @torch.library.register_fake(f"chill_attention::forward{mask_name}")
+    def attention_forward_adapter_abstract(q, k, v, lens, mask_args, sm_scale, return_lse, prescale_qk, precision,
+                                           autotune):
+        return (
+            torch.empty_like(q, memory_format=torch.contiguous_format),
+            torch.empty(q.shape[:3] if return_lse else (0,), dtype=torch.float32, device=q.device),
+        )
+
+    @torch.library.custom_op(f"chill_attention::backward{mask_name}", mutates_args=(), device_types=("cuda",))
+    def attention_backward_adapter(
+        q: torch.Tensor,
+        k: torch.Tensor,
+        v: torch.Tensor,
+        lens: typing.Optional[torch.Tensor],
+        o: torch.Tensor,
+        lse: torch.Tensor,
+        do: torch.Tensor,
+        mask_args: typing.List[typing.Union[int, float, bool]],
+        sm_scale: float,
+        prescale_qk: bool,
+        precision: str,
+        autotune: bool,
+    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        with torch.cuda.device(q.device):
+            delta = torch.empty(o.shape[:-1], dtype=torch.float32, device=o.device)
+            DQ = torch.empty_like(q, memory_format=torch.contiguous_format)
+            DK = torch.empty_like(k, memory_format=torch.contiguous_format)
+            DV = torch.empty_like(v, memory_format=torch.contiguous_format)
+            lens_c = lens.contiguous() if lens is not None else None
+            shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale)
+            _cabi.backward(lib, q, k, v, o, do, lse, delta, DQ, DK, DV, shape)
+        return DQ, DK, DV
+
+    @torch.library.register_fake(f"chill_attention::backward{mask_name}")
+    def attention_backward_adapter_abstract(q, k, v, lens, o, lse, do, mask_args, sm_scale, prescale_qk, precision,
+                                            autotune):
+        return (
+            torch.empty_like(q, memory_format=torch.contiguous_format),
+            torch.empty_like(k, memory_format=torch.contiguous_format),
+            torch.empty_like(v, memory_format=torch.contiguous_format),
+        )
+
+    def setup_context(ctx, inputs, output):
+        O, LSE = output
+        q, k, v, lens, mask_args, sm_scale, return_lse, prescale_qk, precision, autotune = inputs
+        ctx.save_for_backward(q, k, v, O, LSE, lens)
+        ctx.mask_args = mask_args
+        ctx.sm_scale = sm_scale
+        ctx.prescale_qk = prescale_qk
+        ctx.precision = precision
+        ctx.autotune = autotune
+
+    def backward(ctx, do, dlse):
+        # like the reference, no gradient flows through a returned LSE (chill.py:466-490)
+        q, k, v, o, lse, lens = ctx.saved_tensors
+        DQ, DK, DV = attention_backward_adapter(
+            q=q, k=k, v=v, lens=lens, o=o, lse=lse, do=do, mask_args=ctx.mask_args, sm_scale=ctx.sm_scale,
+            prescale_qk=ctx.prescale_qk, precision=ctx.precision, autotune=ctx.autotune,
+        )
+        return DQ, DK, DV, None, None, None, None, None, None, None
+
+    attention_forward_adapter.register_autograd(backward, setup_context=setup_context)
+
+
+def _chill_reference_naive(mask: ChillMask, q, k, v, lens):
+    """Dense-mask PyTorch attention used for testing (reference: chill.py:498-544).
+
+    Returns ``(output * res_mask, res_mask)``; rows at or beyond ``lens[b]`` are zeroed.
+    """
+    import torch.nn.functional as F
+
+    assert q.size(2) == k.size(2)
+    if q.shape[1] != k.shape[1]:
+        group = q.shape[1] // k.shape[1]
+        k = k.repeat_interleave(group, dim=1)
+        v = v.repeat_interleave(group, dim=1)
+    T = q.size(2)
+    attn_mask = mask.make_mask(T, device=q.device)
+    if lens is not None:
+        keep = (torch.arange(T, device=q.device).unsqueeze(0) < lens.unsqueeze(-1)).unsqueeze(-1)
+        attn_mask = attn_mask.unsqueeze(0).unsqueeze(0) & (keep & keep.transpose(-1, -2)).unsqueeze(1)
+        res_mask = keep.unsqueeze(1)
+    else:
+        res_mask = torch.as_tensor(1, device=q.device)
+    return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask) * res_mask, res_mask
+
+
+def _chill_attention(q, k, v, lens, mask_name, mask_args, sm_scale, return_lse, prescale_qk, precision, autotune):
+    requires_grad = any(i.requires_grad for i in (q, k, v))
+    attention_forward = getattr(torch.ops.chill_attention, f"forward{mask_name}")
+    O, LSE = attention_forward(
+        q=q, k=k, v=v, lens=lens, mask_args=mask_args, sm_scale=sm_scale, prescale_qk=prescale_qk,
+        return_lse=return_lse or requires_grad, precision=precision, autotune=autotune,
+    )
+    if return_lse:
+        return O, LSE
+    return O
+
+
+def chill_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    mask: ChillMask,
+    lens: torch.Tensor | None = None,
+    sm_scale: float | None = None,
+    return_lse=False,
+    prescale_qk=False,
+    precision="ieee",
+    autotune=False,
+):
+    """Exact softmax attention restricted to the pairs ``mask`` allows.
+
+    Args:
+        q: [batch, heads, seq_len, head_dim]; k, v: [batch, kv_heads, seq_len, head_dim]
+           (kv_heads divides heads: grouped-query attention).  fp16 / bf16 / fp32, any strides.
+        mask: a ChillMask instance.
+        lens: optional int32 [batch] valid lengths.
+        sm_scale: softmax scale, default head_dim ** -0.5.
+        return_lse: also return the log-sum-exp of every row in log2 units, shape [batch, heads, seq_len].
+        prescale_qk, autotune: accepted for compatibility with the reference, no effect.
+        precision: "ieee" or "tf32"; fp32 inputs are always computed with IEEE fp32 arithmetic.
+
+    Returns: O, or (O, LSE) when ``return_lse``.
+    """
+    register_chill_mask(mask)
+    if not torch.compiler.is_compiling():
+        for i in (q, k, v):
+            torch._dynamo.mark_static(i, 1)
+            torch._dynamo.mark_static(i, 3)
+    if sm_scale is None:
+        sm_scale = 1.0 / (q.shape[-1] ** 0.5)
+    return _chill_attention(
+        q=q, k=k, v=v, lens=lens, mask_name=mask.name, mask_args=mask.constargs, sm_scale=sm_scale,
+        return_lse=return_lse, prescale_qk=prescale_qk, precision=precision, autotune=autotune,
+    )

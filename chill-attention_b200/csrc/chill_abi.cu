@@ -1,0 +1,413 @@
+// C ABI of the library (declared in include/chill_b200.h): argument validation, choice between
+// the tensor-core and the generic kernels, TMA descriptor encoding, launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "bwd_tc.cuh"
+#include "chill_b200.h"
+#include "fwd_tc.cuh"
+#include "generic.cuh"
+#include "tc_launch.h"
+
+namespace chill {
+
+static thread_local char g_cuda_err[256] = "";
+__device__ int g_device_status = 0;
+
+static int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+  return CHILL_E_CUDA;
+}
+
+static int* device_status_ptr() {
+  // one word per device (the symbol is instantiated in every device's module image)
+  int* p = nullptr;
+  if (cudaGetSymbolAddress((void**)&p, g_device_status) != cudaSuccess) return nullptr;
+  return p;
+}
+
+// ------------------------------------------------------------------------- validation
+static size_t esize(int dtype) { return dtype == CHILL_F32 ? 4 : 2; }
+
+static int check_shape(const chill_shape& s) {
+  if (s.B <= 0 || s.H <= 0 || s.H_kv <= 0 || s.Lq <= 0 || s.Lk <= 0 || s.D <= 0) return CHILL_E_INVALID;
+  if (s.H % s.H_kv != 0) return CHILL_E_INVALID;
+  if (s.dtype != CHILL_F32 && s.dtype != CHILL_F16 && s.dtype != CHILL_BF16) return CHILL_E_UNSUPPORTED;
+  if (s.D > kMaxD) return CHILL_E_UNSUPPORTED;
+  if (s.seq_len <= 0 || s.q_offset < 0 || s.k_offset < 0) return CHILL_E_INVALID;
+  if (s.B > 65535 || s.H > 65535) return CHILL_E_TOO_LARGE;
+  if (s.mask.n_args < 0 || s.mask.n_args > CHILL_MAX_MASK_ARGS) return CHILL_E_INVALID;
+#ifdef CHILL_CUSTOM_MASK
+  if (s.mask.id < 0 || s.mask.id > CHILL_MASK_CUSTOM) return CHILL_E_UNSUPPORTED;
+#else
+  if (s.mask.id < 0 || s.mask.id >= CHILL_MASK_CUSTOM) return CHILL_E_UNSUPPORTED;
+#endif
+  if (s.mask.id == CHILL_MASK_CHUNKWISE && (s.mask.n_args < 2 || s.mask.i[0] <= 0)) return CHILL_E_INVALID;
+  if (s.mask.id == CHILL_MASK_SLIDING && s.mask.n_args < 2) return CHILL_E_INVALID;
+  if (s.mask.id == CHILL_MASK_PREFIXLM && s.mask.n_args < 1) return CHILL_E_INVALID;
+  return CHILL_OK;
+}
+
+static MaskArgs to_mask_args(const chill_mask_desc& m) {
+  MaskArgs a;
+  for (int i = 0; i < 8; ++i) {
+    a.i[i] = i < m.n_args ? (int)m.i[i] : 0;
+    a.f[i] = i < m.n_args ? (float)m.f[i] : 0.f;
+  }
+  return a;
+}
+
+static Geo to_geo(const chill_shape& s) {
+  Geo g;
+  g.B = s.B; g.H = s.H; g.Hkv = s.H_kv; g.Lq = s.Lq; g.Lk = s.Lk; g.D = s.D;
+  g.q_off = s.q_offset; g.k_off = s.k_offset; g.seq_len = s.seq_len;
+  g.scale = s.sm_scale; g.lens = s.lens; g.margs = to_mask_args(s.mask);
+  return g;
+}
+
+static TRef to_ref(const void* p, const int64_t* st) {
+  TRef r;
+  r.p = const_cast<void*>(p);
+  r.sb = st[0]; r.sh = st[1]; r.sl = st[2]; r.sd = st[3];
+  return r;
+}
+
+// A [B][H][L][D] tensor can be described to TMA when channels are contiguous and everything
+// else is 16-byte aligned.
+static bool tma_ok(const void* p, const int64_t* st, int B, int H, int L, size_t es) {
+  if (st[3] != 1) return false;
+  if (((uintptr_t)p) % 16 != 0) return false;
+  if ((st[2] * (int64_t)es) % 16 != 0 || st[2] <= 0) return false;
+  if (H > 1 && ((st[1] * (int64_t)es) % 16 != 0 || st[1] <= 0)) return false;
+  if (B > 1 && ((st[0] * (int64_t)es) % 16 != 0 || st[0] <= 0)) return false;
+  (void)L;
+  return true;
+}
+
+static bool shape_tc_ok(const chill_shape& s) {
+  if (s.flags & CHILL_FLAG_FORCE_GENERIC) return false;
+  if (s.dtype != CHILL_F16 && s.dtype != CHILL_BF16) return false;
+  if (s.D != 64 && s.D != 128) return false;
+  if (!(s.sm_scale > 0.f)) return false;
+  return true;
+}
+
+// ------------------------------------------------------------------------ TMA encoding
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// Box = 64 channels x `box_rows` positions of one (batch, head), 128B swizzle.
+static int make_map(CUtensorMap* m, const void* p, const int64_t* st, int B, int H, int L, int D, int dtype,
+                    int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not available");
+    return CHILL_E_CUDA;
+  }
+  const cuuint64_t es = 2;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+  const cuuint64_t row = (cuuint64_t)st[2] * es;
+  cuuint64_t strides[3] = {row, H > 1 ? (cuuint64_t)st[1] * es : row * (cuuint64_t)L,
+                           B > 1 ? (cuuint64_t)st[0] * es : row * (cuuint64_t)L * (cuuint64_t)H};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, dtype == CHILL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void*>(p), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return CHILL_E_CUDA;
+  }
+  return CHILL_OK;
+}
+
+// --------------------------------------------------------------------------- dispatch
+#ifdef CHILL_CUSTOM_MASK
+#define CHILL_CUSTOM_CASE(CALL) \
+  case CHILL_MASK_CUSTOM: { using MaskT = CHILL_CUSTOM_MASK; CALL; break; }
+#else
+#define CHILL_CUSTOM_CASE(CALL)
+#endif
+
+#define CHILL_MASK_SWITCH(ID, CALL)                                        \
+  switch (ID) {                                                            \
+    case CHILL_MASK_FULL: { using MaskT = FullMask; CALL; break; }         \
+    case CHILL_MASK_CAUSAL: { using MaskT = CausalMask; CALL; break; }     \
+    case CHILL_MASK_SLIDING: { using MaskT = SlidingWindowMask; CALL; break; } \
+    case CHILL_MASK_CHUNKWISE: { using MaskT = ChunkwiseMask; CALL; break; } \
+    case CHILL_MASK_PREFIXLM: { using MaskT = PrefixLMMask; CALL; break; } \
+    CHILL_CUSTOM_CASE(CALL)                                                \
+    default: return CHILL_E_UNSUPPORTED;                                   \
+  }
+
+#define CHILL_DTYPE_SWITCH(DT, CALL)                                  \
+  switch (DT) {                                                       \
+    case CHILL_F32: { using ElemT = float; CALL; break; }             \
+    case CHILL_F16: { using ElemT = __half; CALL; break; }            \
+    case CHILL_BF16: { using ElemT = __nv_bfloat16; CALL; break; }    \
+    default: return CHILL_E_UNSUPPORTED;                              \
+  }
+
+static bool fwd_tc_eligible(const chill_fwd_args& a) {
+  const chill_shape& s = a.s;
+  if (!shape_tc_ok(s)) return false;
+  const size_t es = esize(s.dtype);
+  return tma_ok(a.q, a.q_strides, s.B, s.H, s.Lq, es) && tma_ok(a.k, a.k_strides, s.B, s.H_kv, s.Lk, es) &&
+         tma_ok(a.v, a.v_strides, s.B, s.H_kv, s.Lk, es) && tma_ok(a.o, a.o_strides, s.B, s.H, s.Lq, es);
+}
+
+static int check_fwd(const chill_fwd_args* a) {
+  if (a == nullptr) return CHILL_E_INVALID;
+  int st = check_shape(a->s);
+  if (st != CHILL_OK) return st;
+  if (!a->q || !a->k || !a->v || !a->o) return CHILL_E_INVALID;
+  return CHILL_OK;
+}
+
+static int fwd_generic(const chill_fwd_args& a, cudaStream_t st) {
+  FwdP p;
+  p.g = to_geo(a.s);
+  p.q = to_ref(a.q, a.q_strides); p.k = to_ref(a.k, a.k_strides);
+  p.v = to_ref(a.v, a.v_strides); p.o = to_ref(a.o, a.o_strides);
+  p.lse = a.lse;
+  p.lse_sb = a.lse_strides[0]; p.lse_sh = a.lse_strides[1]; p.lse_sl = a.lse_strides[2];
+  dim3 grid((a.s.Lq + kGenericWarps - 1) / kGenericWarps, a.s.H, a.s.B);
+  CHILL_MASK_SWITCH(a.s.mask.id,
+                    CHILL_DTYPE_SWITCH(a.s.dtype, (fwd_generic_kernel<ElemT, MaskT><<<grid, kGenericWarps * 32, 0, st>>>(p))))
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "fwd_generic launch");
+}
+
+static int fwd_tc(const chill_fwd_args& a, cudaStream_t st) {
+  const chill_shape& s = a.s;
+  CUtensorMap maps[4];
+  int rc;
+  if ((rc = make_map(&maps[0], a.q, a.q_strides, s.B, s.H, s.Lq, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+  if ((rc = make_map(&maps[1], a.k, a.k_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+  if ((rc = make_map(&maps[2], a.v, a.v_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+  if ((rc = make_map(&maps[3], a.o, a.o_strides, s.B, s.H, s.Lq, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+  tc::FwdTcParams p;
+  p.g = to_geo(s);
+  p.lse = a.lse;
+  p.lse_sb = a.lse_strides[0]; p.lse_sh = a.lse_strides[1]; p.lse_sl = a.lse_strides[2];
+  p.o = a.o;
+  p.o_sb = a.o_strides[0]; p.o_sh = a.o_strides[1]; p.o_sl = a.o_strides[2];
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
+  dim3 grid((s.Lq + tc::kTile - 1) / tc::kTile, s.H, s.B);
+  int e = 0;
+  CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_fwd<MaskT>(s.dtype, s.D, maps, p, grid, st)))
+  return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "fwd_tc launch");
+}
+
+// ------------------------------------------------------------------------------ backward
+static int check_bwd(const chill_bwd_args* a, bool need_all) {
+  if (a == nullptr) return CHILL_E_INVALID;
+  int st = check_shape(a->s);
+  if (st != CHILL_OK) return st;
+  if (!a->o || !a->d_o || !a->delta) return CHILL_E_INVALID;
+  if (need_all && (!a->q || !a->k || !a->v || !a->lse || !a->dq || !a->dk || !a->dv)) return CHILL_E_INVALID;
+  return CHILL_OK;
+}
+
+static bool bwd_tc_eligible(const chill_bwd_args& a) {
+  if (!tc::kHaveBwdTc) return false;
+  const chill_shape& s = a.s;
+  if (!shape_tc_ok(s)) return false;
+  const size_t es = esize(s.dtype);
+  return tma_ok(a.q, a.q_strides, s.B, s.H, s.Lq, es) && tma_ok(a.k, a.k_strides, s.B, s.H_kv, s.Lk, es) &&
+         tma_ok(a.v, a.v_strides, s.B, s.H_kv, s.Lk, es) && tma_ok(a.d_o, a.do_strides, s.B, s.H, s.Lq, es) &&
+         tma_ok(a.dq, a.dq_strides, s.B, s.H, s.Lq, es) && tma_ok(a.dk, a.dk_strides, s.B, s.H_kv, s.Lk, es) &&
+         tma_ok(a.dv, a.dv_strides, s.B, s.H_kv, s.Lk, es) && a.lse_strides[2] == 1;
+}
+
+static BwdP to_bwdp(const chill_bwd_args& a) {
+  BwdP p;
+  p.g = to_geo(a.s);
+  p.q = to_ref(a.q, a.q_strides); p.k = to_ref(a.k, a.k_strides); p.v = to_ref(a.v, a.v_strides);
+  p.o = to_ref(a.o, a.o_strides); p.d_o = to_ref(a.d_o, a.do_strides);
+  p.dq = to_ref(a.dq, a.dq_strides); p.dk = to_ref(a.dk, a.dk_strides); p.dv = to_ref(a.dv, a.dv_strides);
+  p.lse = a.lse;
+  p.lse_sb = a.lse_strides[0]; p.lse_sh = a.lse_strides[1]; p.lse_sl = a.lse_strides[2];
+  p.delta = a.delta;
+  return p;
+}
+
+static int delta_launch(const chill_bwd_args& a, cudaStream_t st) {
+  const chill_shape& s = a.s;
+  const size_t es = esize(s.dtype);
+  const bool fast = (s.dtype != CHILL_F32) && (s.D == 64 || s.D == 128) &&
+                    tma_ok(a.o, a.o_strides, s.B, s.H, s.Lq, es) && tma_ok(a.d_o, a.do_strides, s.B, s.H, s.Lq, es);
+  if (fast) {
+    const int rows_per_block = 8 * (32 / (s.D / 8));
+    dim3 grid((s.Lq + rows_per_block - 1) / rows_per_block, s.H, s.B);
+#define CHILL_DELTA16(T, DD)                                                                                     \
+  delta_rows16_kernel<T, DD><<<grid, 256, 0, st>>>((const T*)a.o, (const T*)a.d_o, a.delta, a.o_strides[0],        \
+                                                   a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], \
+                                                   a.do_strides[2], s.H, s.Lq)
+    if (s.dtype == CHILL_BF16) {
+      if (s.D == 64) CHILL_DELTA16(__nv_bfloat16, 64); else CHILL_DELTA16(__nv_bfloat16, 128);
+    } else {
+      if (s.D == 64) CHILL_DELTA16(__half, 64); else CHILL_DELTA16(__half, 128);
+    }
+#undef CHILL_DELTA16
+  } else {
+    dim3 grid((s.Lq + kGenericWarps - 1) / kGenericWarps, s.H, s.B);
+    TRef o = to_ref(a.o, a.o_strides), d_o = to_ref(a.d_o, a.do_strides);
+    CHILL_DTYPE_SWITCH(s.dtype, (delta_kernel<ElemT><<<grid, kGenericWarps * 32, 0, st>>>(o, d_o, a.delta, s.H, s.Lq, s.D)))
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "delta launch");
+}
+
+static int bwd_generic(const chill_bwd_args& a, cudaStream_t st) {
+  BwdP p = to_bwdp(a);
+  const chill_shape& s = a.s;
+  dim3 gq((s.Lq + kGenericWarps - 1) / kGenericWarps, s.H, s.B);
+  dim3 gk((s.Lk + kGenericWarps - 1) / kGenericWarps, s.H_kv, s.B);
+  CHILL_MASK_SWITCH(s.mask.id, CHILL_DTYPE_SWITCH(s.dtype, {
+                      (bwd_dq_generic_kernel<ElemT, MaskT><<<gq, kGenericWarps * 32, 0, st>>>(p));
+                      (bwd_dkdv_generic_kernel<ElemT, MaskT><<<gk, kGenericWarps * 32, 0, st>>>(p));
+                    }))
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "bwd_generic launch");
+}
+
+static int bwd_tc(const chill_bwd_args& a, cudaStream_t st) {
+  const chill_shape& s = a.s;
+  CUtensorMap maps[7];
+  const void* ptrs[7] = {a.q, a.k, a.v, a.d_o, a.dq, a.dk, a.dv};
+  const int64_t* strs[7] = {a.q_strides, a.k_strides, a.v_strides, a.do_strides, a.dq_strides, a.dk_strides, a.dv_strides};
+  const bool is_kv[7] = {false, true, true, false, false, true, true};
+  for (int i = 0; i < 7; ++i) {
+    int rc = make_map(&maps[i], ptrs[i], strs[i], s.B, is_kv[i] ? s.H_kv : s.H, is_kv[i] ? s.Lk : s.Lq, s.D, s.dtype,
+                      tc::kTile);
+    if (rc != CHILL_OK) return rc;
+  }
+  tc::BwdTcParams p;
+  p.g = to_geo(s);
+  p.lse = a.lse;
+  p.lse_sb = a.lse_strides[0]; p.lse_sh = a.lse_strides[1]; p.lse_sl = a.lse_strides[2];
+  p.delta = a.delta;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
+  int e = 0;
+  CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd<MaskT>(s.dtype, s.D, maps, p, st)))
+  return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tc launch");
+}
+
+template <class M>
+static int traits_of() {
+  return (M::kHasKFullRange ? 1 : 0) | (M::kHasQFullRange ? 2 : 0) | (M::kKLimsContinuous ? 4 : 0) |
+         (M::kQLimsContinuous ? 8 : 0) | (M::kGuaranteedSafe ? 16 : 0);
+}
+
+}  // namespace chill
+
+using namespace chill;
+
+extern "C" {
+
+int chill_abi_version(void) { return CHILL_ABI_VERSION; }
+
+const char* chill_status_string(int status) {
+  switch (status) {
+    case CHILL_OK: return "ok";
+    case CHILL_E_INVALID: return "invalid argument";
+    case CHILL_E_UNSUPPORTED: return "unsupported dtype, head dim or mask for this build";
+    case CHILL_E_CUDA: return "CUDA call failed";
+    case CHILL_E_TOO_LARGE: return "size exceeds the supported maximum";
+    default: return "unknown status";
+  }
+}
+
+const char* chill_last_cuda_error(void) { return g_cuda_err; }
+
+int chill_fwd_uses_tensor_cores(const chill_fwd_args* a) {
+  int st = check_fwd(a);
+  if (st != CHILL_OK) return st;
+  return fwd_tc_eligible(*a) ? 1 : 0;
+}
+
+int chill_bwd_uses_tensor_cores(const chill_bwd_args* a) {
+  int st = check_bwd(a, true);
+  if (st != CHILL_OK) return st;
+  return bwd_tc_eligible(*a) ? 1 : 0;
+}
+
+int chill_fwd(const chill_fwd_args* a, void* stream) {
+  int st = check_fwd(a);
+  if (st != CHILL_OK) return st;
+  if (fwd_tc_eligible(*a)) return fwd_tc(*a, (cudaStream_t)stream);
+  if (a->s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
+  return fwd_generic(*a, (cudaStream_t)stream);
+}
+
+size_t chill_bwd_scratch_bytes(const chill_shape* s) {
+  if (s == nullptr || s->B <= 0 || s->H <= 0 || s->Lq <= 0) return 0;
+  return (size_t)s->B * (size_t)s->H * (size_t)s->Lq * sizeof(float);
+}
+
+int chill_bwd_delta(const chill_bwd_args* a, void* stream) {
+  int st = check_bwd(a, false);
+  if (st != CHILL_OK) return st;
+  return delta_launch(*a, (cudaStream_t)stream);
+}
+
+int chill_bwd(const chill_bwd_args* a, void* stream) {
+  int st = check_bwd(a, true);
+  if (st != CHILL_OK) return st;
+  if (bwd_tc_eligible(*a)) return bwd_tc(*a, (cudaStream_t)stream);
+  if (a->s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
+  return bwd_generic(*a, (cudaStream_t)stream);
+}
+
+int chill_mask_tabulate(const chill_mask_desc* m, int32_t n, int32_t tile, uint8_t* dense, int32_t* k_lims,
+                        int32_t* q_lims, int32_t* k_full, int32_t* q_full, void* stream) {
+  if (m == nullptr || n <= 0 || tile <= 0 || n > 32768) return CHILL_E_INVALID;
+  MaskArgs a = to_mask_args(*m);
+  const long long total = dense != nullptr ? (long long)n * n : (long long)n;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  cudaStream_t st = (cudaStream_t)stream;
+  CHILL_MASK_SWITCH(m->id, (mask_tabulate_kernel<MaskT><<<blocks, threads, 0, st>>>(a, n, tile, dense, k_lims, q_lims, k_full, q_full)))
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "mask_tabulate launch");
+}
+
+int chill_mask_traits(int32_t mask_id) {
+  CHILL_MASK_SWITCH(mask_id, return traits_of<MaskT>())
+  return CHILL_E_UNSUPPORTED;
+}
+
+int chill_read_device_status(void) {
+  int* p = device_status_ptr();
+  if (p == nullptr) return CHILL_E_CUDA;
+  int v = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail(e, "synchronize");
+  e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(e, "status read");
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return v;
+}
+
+}  // extern "C"

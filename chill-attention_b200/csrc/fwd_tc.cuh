@@ -1,0 +1,334 @@
+// Forward attention on tcgen05 tensor cores (sm_100a), 16-bit inputs, head dim 64 or 128.
+//
+// One CTA owns a tile of 128 query rows of one (batch, head) and walks the key tiles (128 keys
+// each) that the mask functor's range function leaves for it.  Two CTAs share an SM, so one
+// CTA's softmax overlaps the other's MMAs.  Roles inside a CTA (192 threads):
+//
+//   warps 0-3  softmax: thread r owns query row r.  Per key tile: read S row from TMEM,
+//              mask (boundary tiles only), online softmax in base 2, write P (16-bit) back
+//              into the TMEM columns S occupied, rescale the O accumulator in TMEM when the
+//              running max grew by more than 2^8, and finally normalise and store O / LSE.
+//   warp 4     TMA producer: Q once, then K and V tiles into shared-memory rings
+//              (128B-swizzled boxes of 64 channels x 128 rows); owns the TMEM allocation.
+//   warp 5     MMA issuer (one thread): S = Q K^T (both operands from shared memory) and
+//              O += P V (P from TMEM, V from shared memory, MN-major), completion signalled to
+//              mbarriers with tcgen05.commit.
+//
+// TMEM columns: [0,128) S (fp32), overlaid by P (16-bit, columns [0,64)); [128,128+D) O.
+// Reference math: chill_attention/chill_fwd.py:188-359 (three-segment key loop, base-2
+// online softmax, LSE = m + log2 l); the segment split is replaced by a per-tile "full tile"
+// test derived from the functor's k_full_range_for_q.
+#pragma once
+#include "generic.cuh"
+#include "tc_common.cuh"
+
+namespace chill {
+namespace tc {
+
+constexpr int kTile = 128;          // query rows per CTA and keys per tile
+constexpr int kFwdThreads = 192;
+constexpr int kTmemColsFwd = 256;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct FwdTcParams {
+  Geo g;
+  float* lse;
+  long long lse_sb, lse_sh, lse_sl;
+  void* o;  // for zero-filling tiles that are entirely padding
+  long long o_sb, o_sh, o_sl;
+  int* status;
+};
+
+template <int D, int NSTAGE>
+struct FwdSmem {
+  static constexpr int kTileBytes = kTile * D * 2;  // one 128 x D tile of 16-bit elements
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTileBytes;
+  static constexpr int kV = kK + NSTAGE * kTileBytes;
+  static constexpr int kBars = kV + NSTAGE * kTileBytes;
+  static constexpr int kNumBars = 4 + 4 * NSTAGE;
+  static constexpr int kMisc = kBars + 8 * kNumBars;
+  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
+};
+
+// Status codes recorded by bounded waits (1xx = forward).
+enum : int { kStProducer = 101, kStMma = 102, kStSoftmax = 103, kStEpilogue = 104 };
+
+template <typename T, int D, class M, int NSTAGE>
+__global__ void __launch_bounds__(kFwdThreads, 2)
+fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, FwdTcParams p) {
+  using L = FwdSmem<D, NSTAGE>;
+  constexpr int kChunks = D / 64;              // 64-channel (128-byte) column blocks per tile
+  constexpr int kChunkBytes = kTile * 128;     // one column block: 128 rows x 128 bytes
+  const Geo& g = p.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // late (long) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (g.H / g.Hkv);
+  const int qb = qt * kTile;
+  const int qg0 = qb + g.q_off;
+  int n = g.seq_len;
+  if (g.lens != nullptr) n = imin(n, g.lens[b]);
+
+  if (qg0 >= n) {
+    // Every row of this tile is padding: O = 0, LSE = 0 (the reference returns early and leaves
+    // its zero-initialised outputs, chill_fwd.py:70-71).
+    T* obase = reinterpret_cast<T*>(p.o) + b * p.o_sb + h * p.o_sh;
+    const int rows = imin(kTile, g.Lq - qb);
+    for (int idx = threadIdx.x; idx < rows * (D / 8); idx += kFwdThreads) {
+      const int r = idx / (D / 8), c = idx % (D / 8);
+      *reinterpret_cast<uint4*>(obase + (qb + r) * p.o_sl + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+    if (p.lse != nullptr)
+      for (int r = threadIdx.x; r < rows; r += kFwdThreads) p.lse[b * p.lse_sb + h * p.lse_sh + (qb + r) * p.lse_sl] = 0.f;
+    return;
+  }
+
+  // ---- key-tile range of this query tile (same arithmetic in every role)
+  int kt_lo = 0, kt_hi = 0;  // [kt_lo, kt_hi) in units of 128 local key rows
+  int full_lo = 0, full_hi = 0;  // global, half-open: keys visible to every row of the tile
+  {
+    int lo, hi;
+    tile_range<M, true>(qg0, imin(kTile, g.Lq - qb), n, g.margs, lo, hi);
+    const int lo_l = imax(lo - g.k_off, 0);
+    const int hi_l = imin(imin(hi, n - 1) - g.k_off, g.Lk - 1);
+    if (hi_l >= lo_l) {
+      kt_lo = lo_l / kTile;
+      kt_hi = hi_l / kTile + 1;
+    }
+    if (M::kHasKFullRange) M::k_full_range_for_q(qg0, kTile, n, g.margs, full_lo, full_hi);
+  }
+  const int n_tiles = kt_hi - kt_lo;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sQ = base + L::kQ, sK = base + L::kK, sV = base + L::kV;
+  const uint32_t bars = base + L::kBars;
+  const uint32_t bar_q_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_o_full = bars + 24;
+  const uint32_t bar_k_full = bars + 32, bar_k_empty = bar_k_full + 8 * NSTAGE, bar_v_full = bar_k_empty + 8 * NSTAGE,
+                 bar_v_empty = bar_v_full + 8 * NSTAGE;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
+  const Guard guard{p.status, abort_flag};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_p_full, 128);
+    mbar_init(bar_o_full, 1);
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(bar_k_full + 8 * s, 1);
+      mbar_init(bar_k_empty + 8 * s, 1);
+      mbar_init(bar_v_full + 8 * s, 1);
+      mbar_init(bar_v_empty + 8 * s, 1);
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColsFwd);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem;            // S / P columns
+  const uint32_t tO = tmem + kTile;    // O columns
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------- TMA producer
+    if (lane == 0 && n_tiles > 0) {
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      mbar_arrive_expect_tx(bar_q_full, L::kTileBytes);
+      for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * kChunkBytes, &tmQ, bar_q_full, c * 64, qb, h, b);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % NSTAGE;
+        const uint32_t ph = (uint32_t)(j / NSTAGE) & 1u;
+        const int krow = (kt_lo + j) * kTile;
+        ok = mbar_wait(bar_k_empty + 8 * s, ph ^ 1u, guard, kStProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_k_full + 8 * s, L::kTileBytes);
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_4d(sK + s * L::kTileBytes + c * kChunkBytes, &tmK, bar_k_full + 8 * s, c * 64, krow, hk, b);
+        ok = mbar_wait(bar_v_empty + 8 * s, ph ^ 1u, guard, kStProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_v_full + 8 * s, L::kTileBytes);
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_4d(sV + s * L::kTileBytes + c * kChunkBytes, &tmV, bar_v_full + 8 * s, c * 64, krow, hk, b);
+      }
+      if (!ok) {
+        // give copies already in flight time to land before the CTA's shared memory goes away
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 5) {
+    // --------------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
+      constexpr uint32_t idesc_o = make_idesc<T>(kTile, D, false, true);
+      bool ok = mbar_wait(bar_q_full, 0, guard, kStMma);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % NSTAGE;
+        const uint32_t ph = (uint32_t)(j / NSTAGE) & 1u;
+        ok = mbar_wait(bar_k_full + 8 * s, ph, guard, kStMma);
+        if (!ok) break;
+        tc_fence_after();
+        // S = Q K^T: both K-major; 16 channels (32 bytes) per instruction.
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
+          mma_ss(tS, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + s * L::kTileBytes + off, 16, 1024),
+                 idesc_s, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(bar_k_empty + 8 * s);
+        mma_commit(bar_s_full);
+        ok = mbar_wait(bar_p_full, (uint32_t)j & 1u, guard, kStMma);
+        if (!ok) break;
+        ok = mbar_wait(bar_v_full + 8 * s, ph, guard, kStMma);
+        if (!ok) break;
+        tc_fence_after();
+        // O += P V: P (128 x 128, 16-bit) from TMEM, 16 keys = 8 columns per instruction;
+        // V is MN-major: channel blocks 16 KB apart (LBO), 8-key groups 1 KB apart (SBO).
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          mma_ts(tO, tS + kk * 8, smem_desc_sw128(sV + s * L::kTileBytes + kk * 2048, kChunkBytes, 1024), idesc_o,
+                 (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(bar_v_empty + 8 * s);
+      }
+      if (ok) mma_commit(bar_o_full);
+    }
+  } else {
+    // --------------------------------------------------------- softmax + epilogue warps
+    const int r = warp * 32 + lane;  // row inside the tile == TMEM lane
+    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+    const int qg = qg0 + r;
+    const float c = g.scale * kLog2e;
+    float m_used = -CUDART_INF_F, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int kt = kt_lo + j;
+      const int kg0 = kt * kTile + g.k_off;
+      ok = mbar_wait(bar_s_full, (uint32_t)j & 1u, guard, kStSoftmax);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sreg[kTile];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tS + lane_sel + q4 * 32, sreg + q4 * 32);
+      tmem_wait_ld();
+      float* sf = reinterpret_cast<float*>(sreg);
+      const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
+                        kt * kTile + kTile <= g.Lk;
+      if (!full) {
+        const int klim = imin(n - kg0, g.Lk - kt * kTile);  // columns >= klim do not exist
+#pragma unroll
+        for (int cidx = 0; cidx < kTile; ++cidx) {
+          const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
+          sf[cidx] = vis ? sf[cidx] : -CUDART_INF_F;
+        }
+      }
+      float mx = sf[0];
+#pragma unroll
+      for (int cidx = 1; cidx < kTile; ++cidx) mx = fmaxf(mx, sf[cidx]);
+      const float m_tile = mx * c;  // c > 0 (checked by the host)
+      const float m_cand = fmaxf(m_used, m_tile);
+      if (j == 0) {
+        m_used = m_cand;
+      } else {
+        const bool need = (m_cand - m_used) > kRescaleThreshold;  // false when both are -inf
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = (m_cand == -CUDART_INF_F) ? 1.f : ex2(m_used - m_cand);
+          l *= alpha;
+          m_used = m_cand;
+#pragma unroll
+          for (int q4 = 0; q4 < D / 32; ++q4) {
+            uint32_t oreg[32];
+            tmem_ld32(tO + lane_sel + q4 * 32, oreg);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+            tmem_st32(tO + lane_sel + q4 * 32, oreg);
+          }
+        }
+      }
+      const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
+      float lsum = 0.f;
+#pragma unroll
+      for (int cidx = 0; cidx < kTile; ++cidx) {
+        sf[cidx] = ex2(fmaf(sf[cidx], c, -m_safe));
+        lsum += sf[cidx];
+      }
+      l += lsum;
+      uint32_t preg[kTile / 2];
+#pragma unroll
+      for (int i = 0; i < kTile / 2; ++i) preg[i] = pack2<T>(sf[2 * i], sf[2 * i + 1]);
+      tmem_st32(tS + lane_sel, preg);
+      tmem_st32(tS + lane_sel + 32, preg + 32);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p_full);
+    }
+
+    // ---- epilogue: O / l -> 16-bit -> swizzled shared memory (Q's buffer) -> TMA store
+    if (ok && n_tiles > 0) ok = mbar_wait(bar_o_full, 0, guard, kStEpilogue);
+    tc_fence_after();
+    const bool row_valid = qg < n;
+    const float l_safe = (l == 0.f) ? 1.f : l;
+    const float inv = 1.f / l_safe;
+    uint8_t* sO = gen_base + L::kQ;
+#pragma unroll
+    for (int q4 = 0; q4 < D / 32; ++q4) {
+      uint32_t oreg[32];
+      if (n_tiles > 0 && ok) {
+        tmem_ld32(tO + lane_sel + q4 * 32, oreg);
+        tmem_wait_ld();
+      }
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float a = 0.f, bb = 0.f;
+        if (n_tiles > 0 && ok && row_valid && l != 0.f) {
+          a = __uint_as_float(oreg[2 * i]) * inv;
+          bb = __uint_as_float(oreg[2 * i + 1]) * inv;
+        }
+        packed[i] = pack2<T>(a, bb);
+      }
+      // 32 channels = 64 bytes = four 16-byte units of the row's 128-byte line in chunk (q4 / 2)
+      uint8_t* line = sO + (q4 / 2) * kChunkBytes + r * 128;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int unit = ((q4 % 2) * 4 + u) ^ (r & 7);
+        *reinterpret_cast<uint4*>(line + unit * 16) =
+            make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+      }
+    }
+    if (p.lse != nullptr && qb + r < g.Lq) {
+      float v = 0.f;
+      if (row_valid) v = (l == 0.f) ? -CUDART_INF_F : m_used + lg2(l);
+      p.lse[b * p.lse_sb + h * p.lse_sh + (qb + r) * p.lse_sl] = v;
+    }
+    fence_proxy_async_smem();
+    named_bar_sync(1, 128);
+    if (threadIdx.x == 0) {
+      for (int cc = 0; cc < kChunks; ++cc) tma_store_4d(&tmO, base + L::kQ + cc * kChunkBytes, cc * 64, qb, h, b);
+      tma_store_commit();
+      tma_store_wait_all();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem, kTmemColsFwd);
+}
+
+}  // namespace tc
+}  // namespace chill

@@ -1,0 +1,163 @@
+/*
+ * chill_b200.h - C ABI of the B200 (sm_100a) masked flash-attention kernels.
+ *
+ * Every entry point takes plain device pointers, element strides and sizes; none
+ * allocates device memory, synchronises, or keeps state between calls (apart from
+ * a per-process cache of the driver entry point used to encode TMA descriptors).
+ * All work is enqueued on the CUDA stream passed in (a cudaStream_t cast to
+ * void*; NULL = the default stream) of the CURRENT device.  Return value: 0 on
+ * success, a negative CHILL_E_* code otherwise; nothing aborts the process.
+ *
+ * Tensors are indexed [batch][head][position][channel]; `*_strides[4]` are in
+ * ELEMENTS.  The tensor-core path needs channel stride 1 and 16-byte aligned
+ * base / batch / head / position strides for a 16-bit dtype with D in {64,128};
+ * anything else (fp32, other D, odd strides) is served by the generic
+ * kernels of the same library - there is no host fallback.
+ *
+ * Reference counterparts (alexdremov/chill-attention, paths inside that project):
+ *   chill_fwd            replaces the launch of _chill_attn_fwd
+ *                        chill_attention/chill.py:64-211, kernel chill_fwd.py:13-359
+ *   chill_bwd_delta      replaces _chill_attn_bwd_precompute
+ *                        chill_attention/chill.py:261-290, kernel utils.py:93-217
+ *   chill_bwd            replaces the fused launch of _chill_attn_bwd
+ *                        chill_attention/chill.py:292-444, kernels chill_bwd.py:14-168,
+ *                        chill_bwd_dq.py:233-397, chill_bwd_dkdv.py:281-509
+ *   chill_mask_tabulate  replaces ChillMask._mask_infer / _limits_infer /
+ *                        _full_ranges_infer, chill_attention/mask.py:284-377, :487-534
+ */
+#ifndef CHILL_B200_H_
+#define CHILL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CHILL_ABI_VERSION 1
+
+/* status codes */
+#define CHILL_OK 0
+#define CHILL_E_INVALID (-1)      /* null pointer, bad size, H % H_kv != 0, ... */
+#define CHILL_E_UNSUPPORTED (-2)  /* dtype / head dim / mask id this build has no kernel for */
+#define CHILL_E_CUDA (-3)         /* a CUDA runtime/driver call failed; see chill_last_cuda_error */
+#define CHILL_E_TOO_LARGE (-4)    /* a size exceeds what the entry point supports */
+
+/* element types */
+#define CHILL_F32 0
+#define CHILL_F16 1
+#define CHILL_BF16 2
+
+/* built-in mask functors (csrc/masks.cuh); CHILL_MASK_CUSTOM is only present in a
+ * library built with a user functor header */
+#define CHILL_MASK_FULL 0     /* FullChillMask            mask.py:806-889   */
+#define CHILL_MASK_CAUSAL 1   /* CausalChillMask          mask.py:892-976   */
+#define CHILL_MASK_SLIDING 2  /* SlidingWindowChillMask   mask.py:979-1108  args: left, right */
+#define CHILL_MASK_CHUNKWISE 3/* ChunkwiseChillMask       mask.py:1111-1266 args: context_size, back_contexts */
+#define CHILL_MASK_PREFIXLM 4 /* PrefixLMChillMask        mask.py:1269-1394 args: prefix_size */
+#define CHILL_MASK_CUSTOM 5
+
+#define CHILL_MAX_MASK_ARGS 8
+
+/* flags */
+#define CHILL_FLAG_FORCE_GENERIC 1u /* never take the tensor-core path */
+#define CHILL_FLAG_REQUIRE_TC 2u    /* fail with CHILL_E_UNSUPPORTED instead of using the generic path */
+
+/* The mask constants a ChillMask instance was built with (ChillMask.constargs,
+ * mask.py:31-49).  Each is passed both ways: `i[n]` = the value truncated to an
+ * integer, `f[n]` = the value as a double; a functor reads the one it means. */
+typedef struct chill_mask_desc {
+  int32_t id;  /* CHILL_MASK_* */
+  int32_t n_args;
+  int64_t i[CHILL_MAX_MASK_ARGS];
+  double f[CHILL_MAX_MASK_ARGS];
+} chill_mask_desc;
+
+/* Problem geometry shared by forward and backward.
+ *
+ * Query rows are local positions [0, Lq), key rows [0, Lk); the mask functor and
+ * the `lens` bound see GLOBAL positions q + q_offset and k + k_offset, and
+ * `seq_len` is the global sequence length (the value the reference passes to
+ * its mask functions).  A single-device call has Lq == Lk == seq_len and both
+ * offsets 0; a sequence-sharded call passes its shard of the queries, its shard
+ * plus halo of the keys, and the offsets of both.  The reference has no
+ * offsets (chill_fwd.py:141-142 uses local indices).
+ *
+ * `lens` (optional, int32[B], device): valid length of each batch row, clamped
+ * to seq_len.  Keys at global position >= lens[b] are never attended; query rows
+ * at global position >= lens[b] produce O = 0, LSE = 0 and zero gradients. */
+typedef struct chill_shape {
+  int32_t B, H, H_kv, Lq, Lk, D;
+  int32_t dtype; /* CHILL_F32 / CHILL_F16 / CHILL_BF16: q, k, v, o, do, dq, dk, dv */
+  int32_t q_offset, k_offset, seq_len;
+  float sm_scale;
+  uint32_t flags;
+  const int32_t* lens;
+  chill_mask_desc mask;
+} chill_shape;
+
+typedef struct chill_fwd_args {
+  chill_shape s;
+  const void *q, *k, *v;
+  void* o;    /* written for every row of every (b, h) */
+  float* lse; /* optional (may be NULL): log2-domain log-sum-exp, m + log2(l) */
+  int64_t q_strides[4], k_strides[4], v_strides[4], o_strides[4];
+  int64_t lse_strides[3];
+} chill_fwd_args;
+
+typedef struct chill_bwd_args {
+  chill_shape s;
+  const void *q, *k, *v, *o, *d_o;
+  const float* lse; /* from chill_fwd, log2 domain */
+  float* delta;     /* scratch, B*H*Lq floats, contiguous [B][H][Lq]; filled by chill_bwd_delta */
+  void *dq, *dk, *dv; /* written for every row; dk/dv are summed over the GQA group */
+  int64_t q_strides[4], k_strides[4], v_strides[4], o_strides[4], do_strides[4];
+  int64_t dq_strides[4], dk_strides[4], dv_strides[4];
+  int64_t lse_strides[3];
+} chill_bwd_args;
+
+/* O = softmax(mask(Q K^T * sm_scale)) V and LSE.  See chill_shape for conventions. */
+int chill_fwd(const chill_fwd_args* a, void* stream);
+
+/* delta[b,h,t] = sum_d float(O[b,h,t,d]) * float(dO[b,h,t,d]).  Uses a->o, a->d_o, a->delta. */
+int chill_bwd_delta(const chill_bwd_args* a, void* stream);
+
+/* dQ, dK, dV.  a->delta must hold the result of chill_bwd_delta for the same a->o / a->d_o
+ * (enqueue both on the same stream). */
+int chill_bwd(const chill_bwd_args* a, void* stream);
+
+/* Bytes of the `delta` scratch buffer chill_bwd_delta / chill_bwd need. */
+size_t chill_bwd_scratch_bytes(const chill_shape* s);
+
+/* 1 if chill_fwd / chill_bwd would run the tcgen05 tensor-core kernels for these
+ * arguments, 0 if the generic kernels, negative status if the arguments are invalid. */
+int chill_fwd_uses_tensor_cores(const chill_fwd_args* a);
+int chill_bwd_uses_tensor_cores(const chill_bwd_args* a);
+
+/* Tabulate a mask functor on the device (all outputs optional, device pointers):
+ *   dense   uint8[n*n]   mask(q, k) for q, k in [0, n)            (row = query)
+ *   k_lims  int32[n*2]   k_range_for_q(q), inclusive
+ *   q_lims  int32[n*2]   q_range_for_k(k), inclusive
+ *   k_full  int32[ceil(n/tile)*2]  k_full_range_for_q(tile start, tile), half-open
+ *   q_full  int32[ceil(n/tile)*2]  q_full_range_for_k(tile start, tile), half-open
+ * with seq_len = n. */
+int chill_mask_tabulate(const chill_mask_desc* m, int32_t n, int32_t tile, uint8_t* dense, int32_t* k_lims,
+                        int32_t* q_lims, int32_t* k_full, int32_t* q_full, void* stream);
+
+/* Host-side properties of a functor: bit0 has_k_full_range, bit1 has_q_full_range,
+ * bit2 k_lims_continious, bit3 q_lims_continious, bit4 is_guaranteed_safe. */
+int chill_mask_traits(int32_t mask_id);
+
+/* Device-side error word.  Kernels with bounded waits record a non-zero code here instead
+ * of hanging; reading it synchronises the device. Returns the code (0 = none) and clears it. */
+int chill_read_device_status(void);
+
+int chill_abi_version(void);
+const char* chill_status_string(int status);
+const char* chill_last_cuda_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHILL_B200_H_ */

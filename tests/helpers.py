@@ -1,0 +1,99 @@
+"""Shared helpers of the parity tests."""
+import os
+
+import numpy as np
+import torch
+
+from conftest import GOLDEN
+from oracle import attention_oracle as orc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def ensure_built():
+    import __graft_entry__ as ge
+
+    ge.build()
+
+
+def all_masks():
+    import chill_attention as ca
+
+    return [ca.FullChillMask(), ca.CausalChillMask(), ca.SlidingWindowChillMask(10, 4),
+            ca.ChunkwiseChillMask(10, 4), ca.PrefixLMChillMask(10)]
+
+
+def big_masks():
+    """Mask parameters at the scale of the benchmark configurations."""
+    import chill_attention as ca
+
+    return [ca.FullChillMask(), ca.CausalChillMask(), ca.SlidingWindowChillMask(200, 0),
+            ca.SlidingWindowChillMask(100, 60), ca.ChunkwiseChillMask(128, 2), ca.ChunkwiseChillMask(96, 1),
+            ca.PrefixLMChillMask(300)]
+
+
+def make_inputs(B, H, Hkv, L, D, dtype, seed=20):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, L, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, L, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, L, D, generator=g).to(dtype)
+    do = torch.randn(B, H, L, D, generator=g).to(dtype)
+    return q, k, v, do
+
+
+def oracle_all(mask, q, k, v, do, lens=None, sm_scale=None):
+    """fp64 oracle on the (rounded) inputs: O, LSE2, dQ, dK, dV."""
+    L = q.shape[2]
+    pos = torch.arange(L)
+    md = orc.builtin_mask_dense(mask.name, mask.constargs, pos, pos)
+    qd, kd, vd, dod = (t.double() for t in (q, k, v, do))
+    o, lse = orc.attention_forward(md, qd, kd, vd, lens, sm_scale)
+    dq, dk, dv = orc.attention_backward(md, qd, kd, vd, dod, lens, sm_scale)
+    return o, lse, dq, dk, dv
+
+
+def valid_rows(lens, B, L):
+    if lens is None:
+        return torch.ones(B, 1, L, dtype=torch.bool)
+    return torch.arange(L)[None, None, :] < lens.long()[:, None, None]
+
+
+# Output tolerances: max-abs against the fp64 dense-mask oracle evaluated on the same
+# (already rounded) inputs.  16-bit bars are the ones the benchmark specification states;
+# fp32 is the reference test-suite's own bar (test/test_chill_attention.py:167-172).
+O_ATOL = {torch.float32: 5e-6, torch.float16: 1e-2, torch.bfloat16: 2e-2}
+# Gradient tolerance: relative Frobenius norm.
+G_RTOL = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 1e-2}
+
+
+def check_forward(o, lse, o_ref, lse_ref, lens, dtype):
+    B, H, L, _ = o_ref.shape
+    o = o.detach().cpu().double()
+    valid = valid_rows(lens, B, L)
+    err = (o - o_ref).abs().max().item()
+    assert err <= O_ATOL[dtype], f"O max-abs {err}"
+    assert (o[(~valid).expand(B, H, L)] == 0).all(), "padded rows must be exactly zero"
+    if lse is not None:
+        lse = lse.detach().cpu().double()
+        fin = torch.isfinite(lse_ref)
+        assert torch.equal(torch.isfinite(lse), fin), "LSE -inf pattern differs"
+        lerr = ((lse - lse_ref)[fin].abs() / lse_ref[fin].abs().clamp(min=1.0)).max().item() if fin.any() else 0.0
+        assert lerr <= 1e-3, f"LSE error {lerr}"
+        assert (lse[(~valid).expand(B, H, L)] == 0).all()
+
+
+def check_grads(grads, refs, dtype):
+    for name, g, r in zip(("dq", "dk", "dv"), grads, refs):
+        g = g.detach().cpu().double()
+        assert torch.isfinite(g).all(), name
+        denom = r.norm().item()
+        rel = (g - r).norm().item() / denom if denom > 0 else (g - r).norm().item()
+        assert rel <= G_RTOL[dtype], f"{name} relative error {rel}"
+        assert (g[r == 0].abs() <= 1e-6 + (0 if dtype == torch.float32 else 1e-2)).all(), f"{name}: rows that must be zero"
+
+
+def load_golden(name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    t = {k: torch.from_numpy(z[k]) for k in ("q", "k", "v", "do", "o", "lse", "dq", "dk", "dv")}
+    lens = torch.from_numpy(z["lens"]) if z["lens"].size else None
+    return str(z["mask_name"]), tuple(int(a) for a in z["mask_args"]), lens, t

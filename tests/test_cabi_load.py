@@ -1,0 +1,91 @@
+"""The C-ABI library builds, loads without a GPU and exports what include/chill_b200.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from helpers import ROOT, ensure_built
+
+
+@pytest.fixture(scope="module")
+def lib():
+    ensure_built()
+    from chill_attention import _cabi
+
+    return _cabi.load_library()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "chill_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(chill_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_exports(lib):
+    names = declared_functions()
+    assert {"chill_fwd", "chill_bwd", "chill_bwd_delta", "chill_mask_tabulate"} <= set(names)
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    from chill_attention import _cabi
+
+    assert set(_cabi.EXPORTS) <= set(names)
+
+
+def test_struct_sizes_match_header(lib):
+    # sizes computed by hand from the header's field list (LP64)
+    from chill_attention import _cabi
+
+    assert ctypes.sizeof(_cabi.MaskDesc) == 8 + 64 + 64
+    assert ctypes.sizeof(_cabi.Shape) == 56 + 136
+    assert ctypes.sizeof(_cabi.FwdArgs) == 192 + 5 * 8 + 4 * 32 + 24
+    assert ctypes.sizeof(_cabi.BwdArgs) == 192 + 10 * 8 + 8 * 32 + 24
+
+
+def test_host_only_entry_points(lib):
+    assert lib.chill_abi_version() == 1
+    assert lib.chill_status_string(0) == b"ok"
+    assert b"invalid" in lib.chill_status_string(-1)
+    # bit0 k full range, bit1 q full range, bit2/3 continuous limits, bit4 guaranteed safe
+    assert lib.chill_mask_traits(0) == 31 and lib.chill_mask_traits(1) == 31
+    assert lib.chill_mask_traits(2) == 15 and lib.chill_mask_traits(3) == 15 and lib.chill_mask_traits(4) == 31
+    assert lib.chill_mask_traits(9) == -2
+
+
+def test_invalid_arguments_are_rejected_without_a_gpu(lib):
+    from chill_attention import _cabi
+
+    a = _cabi.FwdArgs()
+    assert lib.chill_fwd(ctypes.byref(a), None) == -1          # all-zero shape
+    a.s.B, a.s.H, a.s.H_kv, a.s.Lq, a.s.Lk, a.s.D, a.s.seq_len = 1, 3, 2, 8, 8, 16, 8
+    assert lib.chill_fwd(ctypes.byref(a), None) == -1          # H % H_kv != 0
+    a.s.H = 4
+    a.s.dtype = 7
+    assert lib.chill_fwd(ctypes.byref(a), None) == -2          # unknown dtype
+    a.s.dtype = 0
+    a.s.mask.id = 5
+    assert lib.chill_fwd(ctypes.byref(a), None) == -2          # custom functor not in this build
+    a.s.mask.id = 1
+    assert lib.chill_fwd(ctypes.byref(a), None) == -1          # null pointers
+    s = _cabi.Shape()
+    s.B, s.H, s.Lq = 2, 3, 5
+    assert lib.chill_bwd_scratch_bytes(ctypes.byref(s)) == 2 * 3 * 5 * 4
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    from chill_attention import _cabi
+
+    with pytest.raises(_cabi.ChillLibraryError):
+        _cabi.load_library(str(tmp_path / "nope.so"))
+
+
+def test_no_cuda_means_error_not_fallback(lib):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("needs a machine without a GPU")
+    from chill_attention import CausalChillMask, chill_attention
+
+    q = torch.randn(1, 1, 8, 16)
+    with pytest.raises(Exception):
+        chill_attention(q, q, q, mask=CausalChillMask())
