@@ -1,25 +1,596 @@
-// Backward attention on tcgen05 tensor cores (placeholder until the kernels land).
+// Backward attention on tcgen05 tensor cores (sm_100a), 16-bit inputs, head dim 64 or 128.
+//
+// Two kernels, both with every MMA operand that the softmax math produces kept in TMEM
+// (no shared-memory round trip for P or dS) and no atomics, so results are deterministic:
+//
+//   bwd_dkdv_tc_kernel  one CTA per (batch, kv head, tile of 128 keys).  K and V stay in shared
+//       memory; Q / dO tiles of every query tile that can see the key tile (functor's
+//       q_range_for_k) and of every head of the GQA group stream through a 2-stage TMA ring.
+//       Per query tile:  S^T = K Q^T, dP^T = V dO^T  (TMEM, fp32)
+//                        P^T = 2^(S^T c - LSE),  dS^T = P^T (dP^T - delta)   (registers -> TMEM, 16-bit)
+//                        dV += P^T dO,  dK += dS^T Q   (A from TMEM, B = dO / Q MN-major)
+//       Reference math: chill_attention/chill_bwd_dkdv.py:347-508.
+//
+//   bwd_dq_tc_kernel    one CTA per (batch, head, tile of 128 queries).  Q and dO stay in shared
+//       memory; K / V tiles from the functor's k_range_for_q stream through the ring.
+//       Per key tile:    S = Q K^T, dP = dO V^T;  dS = 2^(S c - LSE) (dP - delta);  dQ += dS K.
+//       Reference math: chill_attention/chill_bwd_dq.py:300-394.
+//
+// Roles in both (320 threads): warps 0-7 do the exponentials (thread (w % 4) * 32 + lane owns
+// TMEM lane = tile row; warps 0-3 take columns 0-63, warps 4-7 columns 64-127), warp 8 is the
+// TMA producer and owns the TMEM allocation, warp 9 issues the MMAs.
 #pragma once
+#include "fwd_tc.cuh"
 #include "generic.cuh"
 #include "tc_common.cuh"
 
 namespace chill {
 namespace tc {
 
+constexpr int kBwdThreads = 320;
+constexpr int kBwdComputeThreads = 256;
+constexpr int kTmemColsBwd = 512;
+constexpr bool kHaveBwdTc = true;
+
 struct BwdTcParams {
   Geo g;
   const float* lse;
   long long lse_sb, lse_sh, lse_sl;
-  const float* delta;
+  const float* delta;  // [B][H][Lq]
+  void *dq, *dk, *dv;  // for zero-filling tiles that are entirely padding
+  long long dq_sb, dq_sh, dq_sl, dk_sb, dk_sh, dk_sl, dv_sb, dv_sh, dv_sl;
   int* status;
 };
 
-template <class M>
-int launch_bwd_all(int, int, const CUtensorMap*, const BwdTcParams&, cudaStream_t) {
-  return -1;  // not built yet: callers use the generic kernels
+template <int D>
+struct BwdSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kStages = 2;
+  static constexpr int kFixA = 0;                      // K (dkdv) or Q (dq)
+  static constexpr int kFixB = kFixA + kTileBytes;     // V (dkdv) or dO (dq)
+  static constexpr int kRing = kFixB + kTileBytes;     // per stage: [Q | dO] (dkdv) or [K | V] (dq)
+  static constexpr int kRows = kRing + kStages * 2 * kTileBytes;  // per compute warp: lse[64], delta[64] floats
+  static constexpr int kBars = kRows + 8 * 2 * 64 * 4;
+  static constexpr int kNumBars = 4 + 2 * kStages;
+  static constexpr int kMisc = kBars + 8 * kNumBars;
+  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+enum : int {
+  kStBwdProducer = 201, kStBwdMma = 202, kStBwdCompute = 203, kStBwdEpilogue = 204,
+  kStDqProducer = 301, kStDqMma = 302, kStDqCompute = 303, kStDqEpilogue = 304
+};
+
+// Zero `rows` rows of D 16-bit channels starting at `base` (row stride `sl` elements).
+template <typename T, int D>
+__device__ __forceinline__ void zero_rows(T* base, long long sl, int rows, int nthreads) {
+  for (int idx = threadIdx.x; idx < rows * (D / 8); idx += nthreads) {
+    const int r = idx / (D / 8), c = idx % (D / 8);
+    *reinterpret_cast<uint4*>(base + r * sl + c * 8) = make_uint4(0, 0, 0, 0);
+  }
 }
 
-constexpr bool kHaveBwdTc = false;
+// Convert 32 fp32 accumulator columns [col0, col0+32) of this thread's row to 16-bit and put them
+// into the row's 128-byte lines of a 128B-swizzled staging tile (layout of a TMA box).
+template <typename T>
+__device__ __forceinline__ void stage_row32(uint8_t* tile, int r, int q4, const uint32_t* acc, float mul, bool keep) {
+  uint32_t packed[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float a = keep ? __uint_as_float(acc[2 * i]) * mul : 0.f;
+    const float b = keep ? __uint_as_float(acc[2 * i + 1]) * mul : 0.f;
+    packed[i] = pack2<T>(a, b);
+  }
+  uint8_t* line = tile + (q4 / 2) * (kTile * 128) + r * 128;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int unit = ((q4 % 2) * 4 + u) ^ (r & 7);
+    *reinterpret_cast<uint4*>(line + unit * 16) =
+        make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+  }
+}
+
+// =========================================================================== dK / dV
+template <typename T, int D, class M>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV, BwdTcParams p) {
+  using L = BwdSmem<D>;
+  constexpr int kChunks = D / 64;
+  constexpr int kChunkBytes = kTile * 128;
+  const Geo& g = p.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = g.H / g.Hkv;
+  const int kb = kt * kTile;
+  const int kg0 = kb + g.k_off;
+  int n = g.seq_len;
+  if (g.lens != nullptr) n = imin(n, g.lens[b]);
+
+  // query-tile range that can see this key tile
+  int qt_lo = 0, qt_hi = 0, full_lo = 0, full_hi = 0;
+  if (kg0 < n) {
+    int lo, hi;
+    tile_range<M, false>(kg0, imin(kTile, g.Lk - kb), n, g.margs, lo, hi);
+    const int lo_l = imax(lo - g.q_off, 0);
+    const int hi_l = imin(imin(hi, n - 1) - g.q_off, g.Lq - 1);
+    if (hi_l >= lo_l) {
+      qt_lo = lo_l / kTile;
+      qt_hi = hi_l / kTile + 1;
+    }
+    if (M::kHasQFullRange) M::q_full_range_for_k(kg0, kTile, n, g.margs, full_lo, full_hi);
+  }
+  const int n_qt = qt_hi - qt_lo;
+  const int n_it = n_qt * G;
+  if (n_it == 0) {
+    // nobody attends these keys (padding, or outside every query's range on this shard)
+    const int rows = imin(kTile, g.Lk - kb);
+    zero_rows<T, D>(reinterpret_cast<T*>(p.dk) + b * p.dk_sb + hk * p.dk_sh + kb * p.dk_sl, p.dk_sl, rows, kBwdThreads);
+    zero_rows<T, D>(reinterpret_cast<T*>(p.dv) + b * p.dv_sb + hk * p.dv_sh + kb * p.dv_sl, p.dv_sl, rows, kBwdThreads);
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sK = base + L::kFixA, sV = base + L::kFixB, sRing = base + L::kRing;
+  float* rows_s = reinterpret_cast<float*>(gen_base + L::kRows);  // [warp][0: lse, 1: delta][64]
+  const uint32_t bars = base + L::kBars;
+  const uint32_t bar_kv_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_acc_full = bars + 24;
+  const uint32_t bar_ring_full = bars + 32, bar_ring_empty = bar_ring_full + 8 * L::kStages;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
+  const Guard guard{p.status, abort_flag};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_kv_full, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_p_full, kBwdComputeThreads);
+    mbar_init(bar_acc_full, 1);
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(bar_ring_full + 8 * s, 1);
+      mbar_init(bar_ring_empty + 8 * s, 1);
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColsBwd);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tSt = tmem, tdPt = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
+
+  if (warp == 8) {
+    // --------------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmdO);
+      mbar_arrive_expect_tx(bar_kv_full, 2 * L::kTileBytes);
+      for (int c = 0; c < kChunks; ++c) {
+        tma_load_4d(sK + c * kChunkBytes, &tmK, bar_kv_full, c * 64, kb, hk, b);
+        tma_load_4d(sV + c * kChunkBytes, &tmV, bar_kv_full, c * 64, kb, hk, b);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it % L::kStages;
+        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+        const int h = hk * G + it / n_qt;
+        const int qrow = (qt_lo + it % n_qt) * kTile;
+        ok = mbar_wait(bar_ring_empty + 8 * s, ph ^ 1u, guard, kStBwdProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_ring_full + 8 * s, 2 * L::kTileBytes);
+        const uint32_t dst = sRing + s * 2 * L::kTileBytes;
+        for (int c = 0; c < kChunks; ++c) {
+          tma_load_4d(dst + c * kChunkBytes, &tmQ, bar_ring_full + 8 * s, c * 64, qrow, h, b);
+          tma_load_4d(dst + L::kTileBytes + c * kChunkBytes, &tmdO, bar_ring_full + 8 * s, c * 64, qrow, h, b);
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 9) {
+    // ----------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
+      constexpr uint32_t idesc_acc = make_idesc<T>(kTile, D, false, true);
+      bool ok = mbar_wait(bar_kv_full, 0, guard, kStBwdMma);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % L::kStages;
+        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+        const uint32_t sQ = sRing + s * 2 * L::kTileBytes, sdO = sQ + L::kTileBytes;
+        ok = mbar_wait(bar_ring_full + 8 * s, ph, guard, kStBwdMma);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {  // S^T = K Q^T
+          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
+          mma_ss(tSt, smem_desc_sw128(sK + off, 16, 1024), smem_desc_sw128(sQ + off, 16, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {  // dP^T = V dO^T
+          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
+          mma_ss(tdPt, smem_desc_sw128(sV + off, 16, 1024), smem_desc_sw128(sdO + off, 16, 1024), idesc_s, kk > 0);
+        }
+        mma_commit(bar_s_full);
+        ok = mbar_wait(bar_p_full, (uint32_t)it & 1u, guard, kStBwdMma);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {  // dV += P^T dO ; dK += dS^T Q   (16 queries per step)
+          const uint32_t acol = (kk / 4) * 64 + (kk % 4) * 8;
+          mma_ts(tdV, tSt + acol, smem_desc_sw128(sdO + kk * 2048, kChunkBytes, 1024), idesc_acc, (it > 0 || kk > 0));
+          mma_ts(tdK, tdPt + acol, smem_desc_sw128(sQ + kk * 2048, kChunkBytes, 1024), idesc_acc, (it > 0 || kk > 0));
+        }
+        mma_commit(bar_ring_empty + 8 * s);
+      }
+      if (ok) mma_commit(bar_acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------------- compute warps
+    const int wg = warp >> 2;                       // column half
+    const int r = (warp & 3) * 32 + lane;           // key row inside the tile == TMEM lane
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const int c0 = wg * 64;
+    const int kg = kg0 + r;
+    const bool key_ok = kg < n && kb + r < g.Lk;
+    const float c = g.scale * kLog2e;
+    const int t = threadIdx.x;  // 0..255
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int h = hk * G + it / n_qt;
+      const int qi = qt_lo + it % n_qt;
+      const int qg0 = qi * kTile + g.q_off;
+      // LSE and delta of this warp's 64 query columns, staged in a warp-private slot (no CTA barrier)
+      float* slot = rows_s + warp * 128;
+      __syncwarp();
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int col = c0 + e * 32 + lane, qrow = qi * kTile + col;
+        float lv = 0.f, dl = 0.f;
+        if (qrow < g.Lq) {
+          lv = p.lse[b * p.lse_sb + h * p.lse_sh + qrow * p.lse_sl];
+          if (lv == -CUDART_INF_F) lv = 0.f;
+          dl = p.delta[((long long)b * g.H + h) * g.Lq + qrow];
+        }
+        slot[e * 32 + lane] = lv;
+        slot[64 + e * 32 + lane] = dl;
+      }
+      __syncwarp();
+      ok = mbar_wait(bar_s_full, (uint32_t)it & 1u, guard, kStBwdCompute);
+      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sreg[64], dpreg[64];
+      tmem_ld32(tSt + lane_sel + c0, sreg);
+      tmem_ld32(tSt + lane_sel + c0 + 32, sreg + 32);
+      tmem_ld32(tdPt + lane_sel + c0, dpreg);
+      tmem_ld32(tdPt + lane_sel + c0 + 32, dpreg + 32);
+      tmem_wait_ld();
+      const bool full = M::kHasQFullRange && qg0 >= full_lo && qg0 + kTile <= full_hi && qg0 + kTile <= n &&
+                        qi * kTile + kTile <= g.Lq && kg0 + kTile <= n && kb + kTile <= g.Lk;
+      const int qlim = imin(n - qg0, g.Lq - qi * kTile);
+      uint32_t preg[32], dsreg[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float pv[2], dv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int col = c0 + 2 * i + e;
+          float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -slot[2 * i + e]));
+          if (!full) {
+            const bool vis = key_ok && col < qlim && M::mask(qg0 + col, kg, n, g.margs);
+            pe = vis ? pe : 0.f;
+          }
+          pv[e] = pe;
+          dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - slot[64 + 2 * i + e]);
+        }
+        preg[i] = pack2<T>(pv[0], pv[1]);
+        dsreg[i] = pack2<T>(dv[0], dv[1]);
+      }
+      tmem_st32(tSt + lane_sel + c0, preg);
+      tmem_st32(tdPt + lane_sel + c0, dsreg);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p_full);
+    }
+
+    // ---- epilogue: warps 0-3 store dV, warps 4-7 store dK * sm_scale (staging = ring stage 0)
+    if (ok) ok = mbar_wait(bar_acc_full, 0, guard, kStBwdEpilogue);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    uint8_t* stage = gen_base + L::kRing + wg * L::kTileBytes;
+    const uint32_t tacc = wg == 0 ? tdV : tdK;
+    const float mul = wg == 0 ? 1.f : g.scale;
+#pragma unroll
+    for (int q4 = 0; q4 < D / 32; ++q4) {
+      uint32_t acc[32];
+      if (ok) {
+        tmem_ld32(tacc + lane_sel + q4 * 32, acc);
+        tmem_wait_ld();
+      }
+      stage_row32<T>(stage, r, q4, acc, mul, ok && key_ok);
+    }
+    fence_proxy_async_smem();
+    named_bar_sync(1, kBwdComputeThreads);
+    if (t == 0 || t == 128) {
+      const CUtensorMap* map = (t == 0) ? &tmdV : &tmdK;
+      for (int cc = 0; cc < kChunks; ++cc)
+        tma_store_4d(map, sRing + wg * L::kTileBytes + cc * kChunkBytes, cc * 64, kb, hk, b);
+      tma_store_commit();
+      tma_store_wait_all();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, kTmemColsBwd);
+}
+
+// ================================================================================ dQ
+template <typename T, int D, class M>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                 const __grid_constant__ CUtensorMap tmdQ, BwdTcParams p) {
+  using L = BwdSmem<D>;
+  constexpr int kChunks = D / 64;
+  constexpr int kChunkBytes = kTile * 128;
+  const Geo& g = p.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (g.H / g.Hkv);
+  const int qb = qt * kTile;
+  const int qg0 = qb + g.q_off;
+  int n = g.seq_len;
+  if (g.lens != nullptr) n = imin(n, g.lens[b]);
+
+  int kt_lo = 0, kt_hi = 0, full_lo = 0, full_hi = 0;
+  if (qg0 < n) {
+    int lo, hi;
+    tile_range<M, true>(qg0, imin(kTile, g.Lq - qb), n, g.margs, lo, hi);
+    const int lo_l = imax(lo - g.k_off, 0);
+    const int hi_l = imin(imin(hi, n - 1) - g.k_off, g.Lk - 1);
+    if (hi_l >= lo_l) {
+      kt_lo = lo_l / kTile;
+      kt_hi = hi_l / kTile + 1;
+    }
+    if (M::kHasKFullRange) M::k_full_range_for_q(qg0, kTile, n, g.margs, full_lo, full_hi);
+  }
+  const int n_it = kt_hi - kt_lo;
+  if (n_it == 0) {
+    zero_rows<T, D>(reinterpret_cast<T*>(p.dq) + b * p.dq_sb + h * p.dq_sh + qb * p.dq_sl, p.dq_sl,
+                    imin(kTile, g.Lq - qb), kBwdThreads);
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sQ = base + L::kFixA, sdO = base + L::kFixB, sRing = base + L::kRing;
+  const uint32_t bars = base + L::kBars;
+  const uint32_t bar_q_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_acc_full = bars + 24;
+  const uint32_t bar_ring_full = bars + 32, bar_ring_empty = bar_ring_full + 8 * L::kStages;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
+  const Guard guard{p.status, abort_flag};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_p_full, kBwdComputeThreads);
+    mbar_init(bar_acc_full, 1);
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(bar_ring_full + 8 * s, 1);
+      mbar_init(bar_ring_empty + 8 * s, 1);
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColsBwd);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      mbar_arrive_expect_tx(bar_q_full, 2 * L::kTileBytes);
+      for (int c = 0; c < kChunks; ++c) {
+        tma_load_4d(sQ + c * kChunkBytes, &tmQ, bar_q_full, c * 64, qb, h, b);
+        tma_load_4d(sdO + c * kChunkBytes, &tmdO, bar_q_full, c * 64, qb, h, b);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it % L::kStages;
+        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+        const int krow = (kt_lo + it) * kTile;
+        ok = mbar_wait(bar_ring_empty + 8 * s, ph ^ 1u, guard, kStDqProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_ring_full + 8 * s, 2 * L::kTileBytes);
+        const uint32_t dst = sRing + s * 2 * L::kTileBytes;
+        for (int c = 0; c < kChunks; ++c) {
+          tma_load_4d(dst + c * kChunkBytes, &tmK, bar_ring_full + 8 * s, c * 64, krow, hk, b);
+          tma_load_4d(dst + L::kTileBytes + c * kChunkBytes, &tmV, bar_ring_full + 8 * s, c * 64, krow, hk, b);
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
+      constexpr uint32_t idesc_acc = make_idesc<T>(kTile, D, false, true);
+      bool ok = mbar_wait(bar_q_full, 0, guard, kStDqMma);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % L::kStages;
+        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+        const uint32_t sK = sRing + s * 2 * L::kTileBytes, sV = sK + L::kTileBytes;
+        ok = mbar_wait(bar_ring_full + 8 * s, ph, guard, kStDqMma);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {  // S = Q K^T
+          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
+          mma_ss(tS, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {  // dP = dO V^T
+          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
+          mma_ss(tdP, smem_desc_sw128(sdO + off, 16, 1024), smem_desc_sw128(sV + off, 16, 1024), idesc_s, kk > 0);
+        }
+        mma_commit(bar_s_full);
+        ok = mbar_wait(bar_p_full, (uint32_t)it & 1u, guard, kStDqMma);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {  // dQ += dS K   (16 keys per step)
+          const uint32_t acol = (kk / 4) * 64 + (kk % 4) * 8;
+          mma_ts(tdQ, tdP + acol, smem_desc_sw128(sK + kk * 2048, kChunkBytes, 1024), idesc_acc, (it > 0 || kk > 0));
+        }
+        mma_commit(bar_ring_empty + 8 * s);
+      }
+      if (ok) mma_commit(bar_acc_full);
+    }
+  } else {
+    const int wg = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;  // query row inside the tile
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const int c0 = wg * 64;
+    const int qg = qg0 + r;
+    const bool row_ok = qg < n && qb + r < g.Lq;
+    const float c = g.scale * kLog2e;
+    float lse = 0.f, delta = 0.f;
+    if (qb + r < g.Lq) {
+      lse = p.lse[b * p.lse_sb + h * p.lse_sh + (qb + r) * p.lse_sl];
+      if (lse == -CUDART_INF_F) lse = 0.f;
+      delta = p.delta[((long long)b * g.H + h) * g.Lq + qb + r];
+    }
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int kt = kt_lo + it;
+      const int kg0 = kt * kTile + g.k_off;
+      ok = mbar_wait(bar_s_full, (uint32_t)it & 1u, guard, kStDqCompute);
+      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sreg[64], dpreg[64];
+      tmem_ld32(tS + lane_sel + c0, sreg);
+      tmem_ld32(tS + lane_sel + c0 + 32, sreg + 32);
+      tmem_ld32(tdP + lane_sel + c0, dpreg);
+      tmem_ld32(tdP + lane_sel + c0 + 32, dpreg + 32);
+      tmem_wait_ld();
+      const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
+                        kt * kTile + kTile <= g.Lk;
+      const int klim = imin(n - kg0, g.Lk - kt * kTile);
+      uint32_t dsreg[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float dv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int col = c0 + 2 * i + e;
+          float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -lse));
+          if (!full) {
+            const bool vis = col < klim && M::mask(qg, kg0 + col, n, g.margs);
+            pe = vis ? pe : 0.f;
+          }
+          pe = row_ok ? pe : 0.f;  // padded query rows contribute nothing and stay finite
+          dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - delta);
+        }
+        dsreg[i] = pack2<T>(dv[0], dv[1]);
+      }
+      tmem_st32(tdP + lane_sel + c0, dsreg);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p_full);
+    }
+
+    // ---- epilogue: dQ * sm_scale; warps 0-3 take channels [0, D/2), warps 4-7 the rest
+    if (ok) ok = mbar_wait(bar_acc_full, 0, guard, kStDqEpilogue);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    uint8_t* stage = gen_base + L::kRing;
+#pragma unroll
+    for (int qq = 0; qq < D / 64; ++qq) {
+      const int q4 = wg * (D / 64) + qq;
+      uint32_t acc[32];
+      if (ok) {
+        tmem_ld32(tdQ + lane_sel + q4 * 32, acc);
+        tmem_wait_ld();
+      }
+      stage_row32<T>(stage, r, q4, acc, g.scale, ok && row_ok);
+    }
+    fence_proxy_async_smem();
+    named_bar_sync(1, kBwdComputeThreads);
+    if (threadIdx.x == 0) {
+      for (int cc = 0; cc < kChunks; ++cc) tma_store_4d(&tmdQ, sRing + cc * kChunkBytes, cc * 64, qb, h, b);
+      tma_store_commit();
+      tma_store_wait_all();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, kTmemColsBwd);
+}
+
+// ---------------------------------------------------------------------------- launchers
+template <typename T, int D, class M>
+int launch_bwd_one(const CUtensorMap* maps, const BwdTcParams& p, cudaStream_t st) {
+  auto kdkdv = bwd_dkdv_tc_kernel<T, D, M>;
+  auto kdq = bwd_dq_tc_kernel<T, D, M>;
+  constexpr int smem = BwdSmem<D>::kDynamic;
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured_dev = dev;
+  }
+  const Geo& g = p.g;
+  // maps: 0 Q, 1 K, 2 V, 3 dO, 4 dQ, 5 dK, 6 dV
+  dim3 gk((g.Lk + kTile - 1) / kTile, g.Hkv, g.B);
+  kdkdv<<<gk, kBwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[5], maps[6], p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  dim3 gq((g.Lq + kTile - 1) / kTile, g.H, g.B);
+  kdq<<<gq, kBwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  return (int)cudaGetLastError();
+}
+
+template <class M>
+int launch_bwd_all(int dtype, int D, const CUtensorMap* maps, const BwdTcParams& p, cudaStream_t st) {
+  if (dtype == 2) {
+    if (D == 128) return launch_bwd_one<__nv_bfloat16, 128, M>(maps, p, st);
+    if (D == 64) return launch_bwd_one<__nv_bfloat16, 64, M>(maps, p, st);
+  } else if (dtype == 1) {
+    if (D == 128) return launch_bwd_one<__half, 128, M>(maps, p, st);
+    if (D == 64) return launch_bwd_one<__half, 64, M>(maps, p, st);
+  }
+  return (int)cudaErrorInvalidValue;
+}
 
 }  // namespace tc
 }  // namespace chill

@@ -304,6 +304,10 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st) {
   p.lse = a.lse;
   p.lse_sb = a.lse_strides[0]; p.lse_sh = a.lse_strides[1]; p.lse_sl = a.lse_strides[2];
   p.delta = a.delta;
+  p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
+  p.dq_sb = a.dq_strides[0]; p.dq_sh = a.dq_strides[1]; p.dq_sl = a.dq_strides[2];
+  p.dk_sb = a.dk_strides[0]; p.dk_sh = a.dk_strides[1]; p.dk_sl = a.dk_strides[2];
+  p.dv_sb = a.dv_strides[0]; p.dv_sh = a.dv_strides[1]; p.dv_sl = a.dv_strides[2];
   p.status = device_status_ptr();
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
   int e = 0;

@@ -219,6 +219,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const int kt = kt_lo + j;
       const int kg0 = kt * kTile + g.k_off;
       ok = mbar_wait(bar_s_full, (uint32_t)j & 1u, guard, kStSoftmax);
+      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
       uint32_t sreg[kTile];
@@ -280,6 +281,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
     // ---- epilogue: O / l -> 16-bit -> swizzled shared memory (Q's buffer) -> TMA store
     if (ok && n_tiles > 0) ok = mbar_wait(bar_o_full, 0, guard, kStEpilogue);
+    ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     const bool row_valid = qg < n;
     const float l_safe = (l == 0.f) ? 1.f : l;

@@ -1,0 +1,159 @@
+"""tcgen05 tensor-core kernels (fp16/bf16, head dim 64/128) against the fp64 dense-mask oracle."""
+import ctypes
+
+import pytest
+import torch
+
+from helpers import all_masks, big_masks, check_forward, check_grads, ensure_built, make_inputs, oracle_all
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib():
+    ensure_built()
+    from chill_attention import _cabi
+
+    lib = _cabi.load_library()
+    yield lib
+    assert lib.chill_read_device_status() == 0
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(_lib):
+    yield
+    assert _lib.chill_read_device_status() == 0, "a bounded wait gave up inside a kernel"
+
+
+def uses_tc(lib, q, k, v, mask):
+    from chill_attention import _cabi
+
+    a = _cabi.FwdArgs()
+    a.s = _cabi.make_shape(q, k, _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor], mask.constargs, None, q.shape[-1] ** -0.5)
+    o = torch.empty_like(q)
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o)):
+        setattr(a, name, (ctypes.c_int64 * 4)(*t.stride()))
+    return lib.chill_fwd_uses_tensor_cores(ctypes.byref(a))
+
+
+def run(mask, q, k, v, do, lens=None, backward=True):
+    from chill_attention import chill_attention
+
+    qd, kd, vd = (t.cuda().requires_grad_(backward) for t in (q, k, v))
+    lens_d = lens.cuda() if lens is not None else None
+    o, lse = chill_attention(qd, kd, vd, mask=mask, lens=lens_d, return_lse=True)
+    grads = None
+    if backward:
+        o.backward(do.cuda())
+        grads = (qd.grad, kd.grad, vd.grad)
+    return o, lse, grads
+
+
+def test_dispatch_takes_the_tensor_core_path(_lib):
+    import chill_attention as ca
+
+    q = torch.zeros(1, 2, 256, 128, dtype=torch.bfloat16, device="cuda")
+    assert uses_tc(_lib, q, q, q, ca.CausalChillMask()) == 1
+    q32 = torch.zeros(1, 2, 256, 128, dtype=torch.float32, device="cuda")
+    assert uses_tc(_lib, q32, q32, q32, ca.CausalChillMask()) == 0
+    q16 = torch.zeros(1, 2, 256, 16, dtype=torch.bfloat16, device="cuda")
+    assert uses_tc(_lib, q16, q16, q16, ca.CausalChillMask()) == 0
+
+
+@pytest.mark.parametrize("mask", big_masks(), ids=str)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("L", [128, 640, 1000])
+def test_forward_backward(mask, dtype, D, L):
+    q, k, v, do = make_inputs(2, 2, 2, L, D, dtype)
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+    o, lse, grads = run(mask, q, k, v, do)
+    check_forward(o, lse, o_ref, lse_ref, None, dtype)
+    check_grads(grads, g_ref, dtype)
+
+
+@pytest.mark.parametrize("mask", all_masks() + big_masks()[2:5], ids=str)
+@pytest.mark.parametrize("heads", [(6, 1), (6, 3), (4, 4)])
+def test_lens_and_gqa(mask, heads):
+    H, Hkv = heads
+    L, dtype = 520, torch.bfloat16
+    q, k, v, do = make_inputs(4, H, Hkv, L, 128, dtype)
+    lens = torch.tensor([L, 1, 130, L + 1], dtype=torch.int32)
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do, lens)
+    o, lse, grads = run(mask, q, k, v, do, lens)
+    check_forward(o, lse, o_ref, lse_ref, lens, dtype)
+    check_grads(grads, g_ref, dtype, lens)
+
+
+@pytest.mark.parametrize("L", [1, 10, 16, 127, 129])
+def test_tiny_sequences(L):
+    import chill_attention as ca
+
+    for mask in (ca.CausalChillMask(), ca.SlidingWindowChillMask(3, 1)):
+        q, k, v, do = make_inputs(2, 2, 1, L, 64, torch.float16)
+        o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+        o, lse, grads = run(mask, q, k, v, do)
+        check_forward(o, lse, o_ref, lse_ref, None, torch.float16)
+        check_grads(grads, g_ref, torch.float16)
+
+
+def test_permuted_layout_blhd():
+    """q/k/v stored [B, L, H, D] and viewed as [B, H, L, D]: still TMA-describable."""
+    import chill_attention as ca
+    from chill_attention import chill_attention
+
+    mask = ca.CausalChillMask()
+    q, k, v, do = make_inputs(2, 4, 4, 300, 128, torch.bfloat16)
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+    qd, kd, vd = (t.transpose(1, 2).contiguous().cuda().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+    assert not qd.is_contiguous()
+    o, lse = chill_attention(qd, kd, vd, mask=mask, return_lse=True)
+    o.backward(do.cuda())
+    check_forward(o, lse, o_ref, lse_ref, None, torch.bfloat16)
+    check_grads((qd.grad, kd.grad, vd.grad), g_ref, torch.bfloat16)
+
+
+def test_deterministic():
+    import chill_attention as ca
+
+    mask = ca.PrefixLMChillMask(100)
+    q, k, v, do = make_inputs(1, 4, 4, 700, 128, torch.bfloat16)
+    a = run(mask, q, k, v, do)
+    b = run(mask, q, k, v, do)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_large_magnitude_scores_rescale_path():
+    """Scores whose running maximum keeps growing by more than the lazy-rescale threshold."""
+    import chill_attention as ca
+
+    mask = ca.FullChillMask()
+    q, k, v, do = make_inputs(1, 1, 1, 1024, 128, torch.bfloat16)
+    ramp = torch.linspace(0.2, 6.0, 1024).reshape(1, 1, 1024, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)  # later keys have larger norms -> the max moves tile after tile
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+    o, lse, grads = run(mask, q, k, v, do)
+    check_forward(o, lse, o_ref, lse_ref, None, torch.bfloat16)
+    check_grads(grads, g_ref, torch.bfloat16)
+
+
+def test_torch_compile_traces_the_op():
+    import chill_attention as ca
+    from chill_attention import chill_attention
+
+    mask = ca.CausalChillMask()
+    q, k, v, do = make_inputs(1, 2, 2, 256, 64, torch.bfloat16)
+
+    def f(q, k, v):
+        return chill_attention(q, k, v, mask=mask) * 2.0
+
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    eager = f(qd, kd, vd)
+    compiled = torch.compile(f, fullgraph=True)(qd, kd, vd)
+    assert torch.equal(eager, compiled)
+    compiled.backward(do.cuda())
+    assert qd.grad is not None and torch.isfinite(qd.grad).all()
+    torch.library.opcheck(torch.ops.chill_attention.forwardCausalChillMask.default,
+                          (qd.detach(), kd.detach(), vd.detach(), None, [], 0.125, True, False, "ieee", False),
+                          test_utils=("test_schema", "test_faketensor"))
