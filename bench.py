@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the masked-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+
+One "step" is one forward + backward pass (forward, delta, dK/dV, dQ kernels) over one
+synthetic batch of the workload.  The default workload is the configuration the headline
+metric is quoted on: CausalChillMask, bf16, (B, H, L, D) = (8, 16, 4096, 128), inputs ~N(0,1)
+seeded, sm_scale = D**-0.5.  Other workloads (c3, c4, c5 ...) are for kernel work, not for the
+reported line.
+
+Reported (one JSON line on rank 0):
+  value        effective TFLOP/s of forward+backward counting only unmasked (q, k) pairs:
+               14 * B * H * D * pairs FLOPs per step (4 fwd + 10 bwd), inputs resident in HBM,
+               timed with CUDA events on the launching stream, max over ranks.
+  fwd / fwd_bwd / pct_of_peak   the forward-only number and both as a share of the measured
+               dense bf16 peak (MEASURED_PEAKS.json) and of the nominal 2250 TFLOP/s.
+  roofline     dominant kernel (largest share of the step): algorithmic FLOPs / its mean
+               CUDA-event duration, against the measured cuBLAS bf16 peak.
+  e2e          the same metric through the public API (chill_attention + autograd) with HOST
+               buffers: per step q, k, v, dO are copied from pinned host memory and O, dQ, dK,
+               dV are copied back, all inside the timed region.
+  cpu_baseline the CPU oracle (dense-mask fp32 attention, fwd + closed-form bwd) timed on the
+               host cores on a bounded sample of the same workload.
+
+Multi-GPU (torchrun, one rank per GPU): every rank runs the workload on its own shard of the
+batch x head units - no data-path collective; per-GPU work is fixed ("weak").  Workload c5
+with --gpus > 1 is sequence-sharded instead (K/V halo over NCCL send/recv).
+
+`--impl reference` times the reference's CPU path (dense boolean mask + fp32 attention, the
+oracle port of its `_chill_reference_naive` with closed-form gradients) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "chill-attention_b200"), ROOT):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+METRIC = "effective TFLOP/s (unmasked FLOPs) fwd & fwd+bwd, % of B200 dense BF16 peak"
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+WORKLOADS = {
+    # name: (mask class, mask args, dtype, B, H, L, D)
+    "c1": ("CausalChillMask", (), "float32", 1, 2, 128, 64),
+    "c2": ("CausalChillMask", (), "bfloat16", 8, 16, 4096, 128),
+    "c3": ("ChunkwiseChillMask", (128, 2), "float16", 4, 32, 16384, 64),
+    "c4": ("PrefixLMChillMask", (1024,), "bfloat16", 4, 16, 8192, 128),
+    "c5": ("SlidingWindowChillMask", (1024, 0), "bfloat16", 1, 32, 131072, 128),
+    "full": ("FullChillMask", (), "bfloat16", 8, 16, 4096, 128),
+    # c2 with a quarter of the batch: same kernels and tile counts per CTA, small enough for an ncu capture
+    "c2s": ("CausalChillMask", (), "bfloat16", 2, 16, 4096, 128),
+}
+
+
+def describe(name):
+    m, a, dt, B, H, L, D = WORKLOADS[name]
+    return f"{name}: {m}{a} fwd+bwd {dt} (B={B},H={H},L={L},D={D}), N(0,1) inputs, sm_scale=D^-0.5"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return FALLBACK_BF16_TFLOPS, 1400.0, "fallback"
+
+
+def unmasked_pairs(mask, L):
+    """Visible (q, k) pairs per head: every built-in mask row is one contiguous key interval."""
+    pos = torch.arange(L, dtype=torch.int64)
+    lo, hi = type(mask).k_range_for_q(pos, L, mask.constargs)
+    lo = torch.as_tensor(lo).expand(L)
+    hi = torch.as_tensor(hi).expand(L)
+    return int((hi - lo + 1).clamp(min=0).sum())
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.idx = device_index
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, reasons, maxc = [], set(), None
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                clocks.append(float(f[1]))
+                maxc = float(f[2])
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        if clocks:
+            busy = [c for c in clocks if c > 0.5 * max(clocks)] or clocks
+            self.result = {"sm_mhz": statistics.median(busy), "sm_max_mhz": maxc, "reasons": sorted(reasons),
+                           "samples": len(clocks)}
+
+
+def make_host_inputs(name, B, seed):
+    _, _, dt, _, H, L, D = WORKLOADS[name]
+    dtype = getattr(torch, dt)
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(B, H, L, D, generator=g, dtype=torch.float32).to(dtype) for _ in range(4)]
+
+
+# --------------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import torch.distributed as dist
+
+    import chill_attention as ca
+    from chill_attention import _cabi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "c5" and world > 1:
+        from chill_attention import dist as cdist  # sequence-sharded path
+
+        return cdist.bench_sequence_sharded(args, WORKLOADS["c5"], METRIC)
+
+    mname, margs, dt, B, H, L, D = WORKLOADS[args.workload]
+    dtype = getattr(torch, dt)
+    mask = getattr(ca, mname)(*margs)
+    lib = _cabi.load_library()
+    functor = _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor]
+    scale = D ** -0.5
+    pairs = unmasked_pairs(mask, L)
+    flops_fwd = 4.0 * B * H * D * pairs
+    flops_step = 14.0 * B * H * D * pairs
+
+    # ---- device-resident inputs (generated on the device: throughput run)
+    g = torch.Generator(device=dev).manual_seed(20 + rank)
+    q, k, v, do = (torch.randn(B, H, L, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4))
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, L, dtype=torch.float32, device=dev)
+    delta = torch.empty(B, H, L, dtype=torch.float32, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    shape = _cabi.make_shape(q, k, functor, margs, None, scale)
+    shape_dkdv = _cabi.make_shape(q, k, functor, margs, None, scale, flags=_cabi.FLAG_BWD_ONLY_DKDV)
+    shape_dq = _cabi.make_shape(q, k, functor, margs, None, scale, flags=_cabi.FLAG_BWD_ONLY_DQ)
+    import ctypes as C
+
+    bargs_dkdv = _cabi.backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape_dkdv)
+    bargs_dq = _cabi.backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape_dq)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    kernels = ("fwd", "delta", "dkdv", "dq")
+
+    def step(events=None):
+        if events is not None:
+            events[0].record()
+        _cabi.forward(lib, q, k, v, o, lse, shape)
+        if events is not None:
+            events[1].record()
+        _cabi.check(lib, lib.chill_bwd_delta(C.byref(bargs_dkdv), stream), "chill_bwd_delta")
+        if events is not None:
+            events[2].record()
+        _cabi.check(lib, lib.chill_bwd(C.byref(bargs_dkdv), stream), "chill_bwd(dkdv)")
+        if events is not None:
+            events[3].record()
+        _cabi.check(lib, lib.chill_bwd(C.byref(bargs_dq), stream), "chill_bwd(dq)")
+        if events is not None:
+            events[4].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    with ClockSampler(local) as clk:
+        barrier()
+        t_host0 = time.perf_counter()
+        for i in range(args.steps):
+            step(evs[i])
+        barrier()
+        t_host1 = time.perf_counter()
+    total_ms = evs[0][0].elapsed_time(evs[-1][4])
+    per_kernel = {kn: sum(e[i].elapsed_time(e[i + 1]) for e in evs) / args.steps for i, kn in enumerate(kernels)}
+    fwd_ms = per_kernel["fwd"]
+    status = lib.chill_read_device_status()
+    if status != 0:
+        raise SystemExit(f"device status {status}: a kernel gave up on a bounded wait")
+    uses_tc = lib.chill_bwd_uses_tensor_cores(C.byref(bargs_dq))
+
+    # ---- end to end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        host = [t.pin_memory() for t in make_host_inputs(args.workload, B, 20 + rank)]
+        out_host = [torch.empty(B, H, L, D, dtype=dtype).pin_memory() for _ in range(4)]
+        dq_, dk_, dv_ = None, None, None
+
+        def e2e_step():
+            qd, kd, vd, dod = (t.to(dev, non_blocking=True) for t in host)
+            qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True)
+            od = ca.chill_attention(qd, kd, vd, mask=mask)
+            od.backward(dod)
+            for dst, src in zip(out_host, (od.detach(), qd.grad, kd.grad, vd.grad)):
+                dst.copy_(src, non_blocking=True)
+
+        for _ in range(max(1, min(args.warmup, 3))):
+            e2e_step()
+        barrier()
+        n_e2e = max(2, min(args.steps, 10))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / n_e2e
+        esz = q.element_size()
+        e2e = {"ms_per_step": e2e_ms, "h2d": 4 * B * H * L * D * esz, "d2h": 4 * B * H * L * D * esz}
+
+    # ---- max over ranks
+    times = torch.tensor([total_ms, fwd_ms, e2e["ms_per_step"] if e2e else 0.0] + [per_kernel[k_] for k_ in kernels],
+                         dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, fwd_ms, e2e_ms = times[0].item(), times[1].item(), times[2].item()
+    per_kernel = {kn: times[3 + i].item() for i, kn in enumerate(kernels)}
+
+    if rank == 0:
+        peak, peak_sustained, peak_src = measured_peaks()
+        ms_per_step = total_ms / args.steps
+        value = world * flops_step / (ms_per_step * 1e-3) / 1e12
+        fwd_tflops = world * flops_fwd / (fwd_ms * 1e-3) / 1e12
+        kflops = {"fwd": 4.0, "dkdv": 8.0, "dq": 6.0}
+        dom = max(("fwd", "dkdv", "dq"), key=lambda kn: per_kernel[kn])
+        achieved = kflops[dom] * B * H * D * pairs / (per_kernel[dom] * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dt == "bfloat16" else ("f16" if dt == "float16" else "f32"),
+            "data": "synthetic: seeded N(0,1) q,k,v,dO of the workload's shape; no dataset is involved",
+            "config": {"workload": describe(args.workload), "global_batch": B * world, "seq_len": L,
+                       "parallelism": f"batch x head units sharded over {world} GPU(s), no collective",
+                       "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no explicit flush"
+                             % (8 * B * H * L * D * q.element_size() / 1e6),
+                       "tensor_core_path": bool(uses_tc == 1)},
+            "fwd": {"tflops": round(fwd_tflops, 2), "ms": round(fwd_ms, 4),
+                    "pct_of_measured_peak": round(100 * fwd_tflops / world / peak, 2),
+                    "pct_of_nominal_peak": round(100 * fwd_tflops / world / NOMINAL_BF16_TFLOPS, 2)},
+            "fwd_bwd": {"tflops": round(value, 2), "pct_of_measured_peak": round(100 * value / world / peak, 2),
+                        "pct_of_nominal_peak": round(100 * value / world / NOMINAL_BF16_TFLOPS, 2)},
+            "kernel_ms": {kn: round(per_kernel[kn], 4) for kn in kernels},
+            "roofline": {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 2), "peak": peak,
+                         "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
+                         "peak_source": f"{peak_src} cuBLAS bf16 burst (sustained {peak_sustained})",
+                         "flops_per_launch": kflops[dom] * B * H * D * pairs},
+            "gpu_launches": 4 * args.steps,
+            "clocks": clk.result,
+            "host_wall_ms_per_step": round((t_host1 - t_host0) * 1e3 / args.steps, 4),
+        }
+        if e2e:
+            line["e2e"] = {"value": round(world * flops_step / (e2e_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s",
+                           "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                           "ms_per_step": round(e2e_ms, 3)}
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=args.cpu_budget)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_pass(name, n_units, seed=20):
+    """fwd + bwd of `n_units` (batch, head) units of the workload with the CPU oracle. Returns seconds."""
+    from oracle import attention_oracle as orc
+
+    mname, margs, dt, B, H, L, D = WORKLOADS[name]
+    g = torch.Generator().manual_seed(seed)
+    dtype = getattr(torch, dt)
+    q, k, v, do = (torch.randn(1, n_units, L, D, generator=g).to(dtype).float() for _ in range(4))
+    t0 = time.perf_counter()
+    if L <= 8192:
+        pos = torch.arange(L)
+        md = orc.builtin_mask_dense(mname, margs, pos, pos)
+        for u in range(n_units):
+            sl = slice(u, u + 1)
+            orc.attention_forward(md, q[:, sl], k[:, sl], v[:, sl], dtype=torch.float32)
+            orc.attention_backward(md, q[:, sl], k[:, sl], v[:, sl], do[:, sl], dtype=torch.float32)
+    else:
+        orc.banded_forward(mname, margs, q, k, v, dtype=torch.float32)
+        orc.banded_backward(mname, margs, q, k, v, do, dtype=torch.float32)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(name, budget_s=15.0):
+    import chill_attention as ca
+
+    mname, margs, dt, B, H, L, D = WORKLOADS[name]
+    mask = getattr(ca, mname)(*margs)
+    pairs = unmasked_pairs(mask, L)
+    t1 = cpu_pass(name, 1)
+    units = max(1, min(B * H, int(budget_s / max(t1, 1e-3))))
+    t = cpu_pass(name, units) if units > 1 else t1
+    tflops = 14.0 * units * D * pairs / t / 1e12
+    return {"value": round(tflops, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{units} of {B * H} (batch, head) units of the workload, fp32 dense-mask attention fwd + "
+                      f"closed-form bwd (oracle/attention_oracle.py), {t:.2f} s",
+            "seconds": round(t, 3), "units": units}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import chill_attention as ca
+
+    mname, margs, dt, B, H, L, D = WORKLOADS[args.workload]
+    mask = getattr(ca, mname)(*margs)
+    pairs = unmasked_pairs(mask, L)
+    t1 = cpu_pass(args.workload, 1)
+    # size a step so that warmup + steps stay within a few minutes
+    units = max(1, min(B * H, int(args.cpu_budget / max(t1, 1e-3))))
+    for _ in range(args.warmup):
+        cpu_pass(args.workload, units)
+    ts = [cpu_pass(args.workload, units) for _ in range(args.steps)]
+    t = sum(ts) / len(ts)
+    value = 14.0 * units * D * pairs / t / 1e12
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 5), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t * 1e3, 2), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic: seeded N(0,1)",
+        "config": {"workload": describe(args.workload), "global_batch": B, "seq_len": L,
+                   "parallelism": "host cores only (rank 0)"},
+        "cpu_baseline": {"value": round(value, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"each step = {units} of {B * H} (batch, head) units, fp32 dense-mask attention "
+                                   f"fwd + closed-form bwd on the host (the reference's CPU path restated in "
+                                   f"oracle/attention_oracle.py; its Triton kernels have no timed CPU mode)"},
+        "e2e": {"value": round(value, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work per baseline sample")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -40,6 +40,7 @@ struct BwdTcParams {
   void *dq, *dk, *dv;  // for zero-filling tiles that are entirely padding
   long long dq_sb, dq_sh, dq_sl, dk_sb, dk_sh, dk_sl, dv_sb, dv_sh, dv_sl;
   int* status;
+  int which;  // bit0: launch the dK/dV kernel, bit1: launch the dQ kernel
 };
 
 template <int D>
@@ -571,12 +572,16 @@ int launch_bwd_one(const CUtensorMap* maps, const BwdTcParams& p, cudaStream_t s
   }
   const Geo& g = p.g;
   // maps: 0 Q, 1 K, 2 V, 3 dO, 4 dQ, 5 dK, 6 dV
-  dim3 gk((g.Lk + kTile - 1) / kTile, g.Hkv, g.B);
-  kdkdv<<<gk, kBwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[5], maps[6], p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  dim3 gq((g.Lq + kTile - 1) / kTile, g.H, g.B);
-  kdq<<<gq, kBwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  if (p.which & 1) {
+    dim3 gk((g.Lk + kTile - 1) / kTile, g.Hkv, g.B);
+    kdkdv<<<gk, kBwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[5], maps[6], p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (p.which & 2) {
+    dim3 gq((g.Lq + kTile - 1) / kTile, g.H, g.B);
+    kdq<<<gq, kBwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  }
   return (int)cudaGetLastError();
 }
 

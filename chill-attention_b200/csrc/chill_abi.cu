@@ -275,14 +275,21 @@ static int delta_launch(const chill_bwd_args& a, cudaStream_t st) {
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "delta launch");
 }
 
+static int bwd_which(uint32_t flags) {
+  if (flags & CHILL_FLAG_BWD_ONLY_DKDV) return 1;
+  if (flags & CHILL_FLAG_BWD_ONLY_DQ) return 2;
+  return 3;
+}
+
 static int bwd_generic(const chill_bwd_args& a, cudaStream_t st) {
   BwdP p = to_bwdp(a);
   const chill_shape& s = a.s;
+  const int which = bwd_which(s.flags);
   dim3 gq((s.Lq + kGenericWarps - 1) / kGenericWarps, s.H, s.B);
   dim3 gk((s.Lk + kGenericWarps - 1) / kGenericWarps, s.H_kv, s.B);
   CHILL_MASK_SWITCH(s.mask.id, CHILL_DTYPE_SWITCH(s.dtype, {
-                      (bwd_dq_generic_kernel<ElemT, MaskT><<<gq, kGenericWarps * 32, 0, st>>>(p));
-                      (bwd_dkdv_generic_kernel<ElemT, MaskT><<<gk, kGenericWarps * 32, 0, st>>>(p));
+                      if (which & 2) (bwd_dq_generic_kernel<ElemT, MaskT><<<gq, kGenericWarps * 32, 0, st>>>(p));
+                      if (which & 1) (bwd_dkdv_generic_kernel<ElemT, MaskT><<<gk, kGenericWarps * 32, 0, st>>>(p));
                     }))
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "bwd_generic launch");
@@ -310,6 +317,7 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st) {
   p.dv_sb = a.dv_strides[0]; p.dv_sh = a.dv_strides[1]; p.dv_sl = a.dv_strides[2];
   p.status = device_status_ptr();
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
+  p.which = bwd_which(s.flags);
   int e = 0;
   CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd<MaskT>(s.dtype, s.D, maps, p, st)))
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tc launch");

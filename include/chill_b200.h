@@ -63,6 +63,8 @@ extern "C" {
 /* flags */
 #define CHILL_FLAG_FORCE_GENERIC 1u /* never take the tensor-core path */
 #define CHILL_FLAG_REQUIRE_TC 2u    /* fail with CHILL_E_UNSUPPORTED instead of using the generic path */
+#define CHILL_FLAG_BWD_ONLY_DKDV 4u /* chill_bwd launches only the dK/dV kernel (per-kernel timing) */
+#define CHILL_FLAG_BWD_ONLY_DQ 8u   /* chill_bwd launches only the dQ kernel */
 
 /* The mask constants a ChillMask instance was built with (ChillMask.constargs,
  * mask.py:31-49).  Each is passed both ways: `i[n]` = the value truncated to an
