@@ -270,35 +270,36 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
-      uint32_t sreg[64], dpreg[64];
-      tmem_ld32(tSt + lane_sel + c0, sreg);
-      tmem_ld32(tSt + lane_sel + c0 + 32, sreg + 32);
-      tmem_ld32(tdPt + lane_sel + c0, dpreg);
-      tmem_ld32(tdPt + lane_sel + c0 + 32, dpreg + 32);
-      tmem_wait_ld();
       const bool full = M::kHasQFullRange && qg0 >= full_lo && qg0 + kTile <= full_hi && qg0 + kTile <= n &&
                         qi * kTile + kTile <= g.Lq && kg0 + kTile <= n && kb + kTile <= g.Lk;
       const int qlim = imin(n - qg0, g.Lq - qi * kTile);
-      uint32_t preg[32], dsreg[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float pv[2], dv[2];
+      for (int ch = 0; ch < 2; ++ch) {  // 32 query columns at a time
+        uint32_t sreg[32], dpreg[32], preg[16], dsreg[16];
+        tmem_ld32(tSt + lane_sel + c0 + ch * 32, sreg);
+        tmem_ld32(tdPt + lane_sel + c0 + ch * 32, dpreg);
+        tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int col = c0 + 2 * i + e;
-          float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -slot[2 * i + e]));
-          if (!full) {
-            const bool vis = key_ok && col < qlim && M::mask(qg0 + col, kg, n, g.margs);
-            pe = vis ? pe : 0.f;
+        for (int i = 0; i < 16; ++i) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int cw = ch * 32 + 2 * i + e;  // column inside this warp's 64
+            float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -slot[cw]));
+            if (!full) {
+              const bool vis = key_ok && c0 + cw < qlim && M::mask(qg0 + c0 + cw, kg, n, g.margs);
+              pe = vis ? pe : 0.f;
+            }
+            pv[e] = pe;
+            dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - slot[64 + cw]);
           }
-          pv[e] = pe;
-          dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - slot[64 + 2 * i + e]);
+          preg[i] = pack2<T>(pv[0], pv[1]);
+          dsreg[i] = pack2<T>(dv[0], dv[1]);
         }
-        preg[i] = pack2<T>(pv[0], pv[1]);
-        dsreg[i] = pack2<T>(dv[0], dv[1]);
+        // 16-bit P^T / dS^T over the fp32 columns just consumed (own column range only)
+        tmem_st16(tSt + lane_sel + c0 + ch * 16, preg);
+        tmem_st16(tdPt + lane_sel + c0 + ch * 16, dsreg);
       }
-      tmem_st32(tSt + lane_sel + c0, preg);
-      tmem_st32(tdPt + lane_sel + c0, dsreg);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full);
@@ -493,33 +494,33 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
-      uint32_t sreg[64], dpreg[64];
-      tmem_ld32(tS + lane_sel + c0, sreg);
-      tmem_ld32(tS + lane_sel + c0 + 32, sreg + 32);
-      tmem_ld32(tdP + lane_sel + c0, dpreg);
-      tmem_ld32(tdP + lane_sel + c0 + 32, dpreg + 32);
-      tmem_wait_ld();
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
                         kt * kTile + kTile <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * kTile);
-      uint32_t dsreg[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float dv[2];
+      for (int ch = 0; ch < 2; ++ch) {  // 32 key columns at a time
+        uint32_t sreg[32], dpreg[32], dsreg[16];
+        tmem_ld32(tS + lane_sel + c0 + ch * 32, sreg);
+        tmem_ld32(tdP + lane_sel + c0 + ch * 32, dpreg);
+        tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int col = c0 + 2 * i + e;
-          float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -lse));
-          if (!full) {
-            const bool vis = col < klim && M::mask(qg, kg0 + col, n, g.margs);
-            pe = vis ? pe : 0.f;
+        for (int i = 0; i < 16; ++i) {
+          float dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c0 + ch * 32 + 2 * i + e;
+            float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -lse));
+            if (!full) {
+              const bool vis = col < klim && M::mask(qg, kg0 + col, n, g.margs);
+              pe = vis ? pe : 0.f;
+            }
+            pe = row_ok ? pe : 0.f;  // padded query rows contribute nothing and stay finite
+            dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - delta);
           }
-          pe = row_ok ? pe : 0.f;  // padded query rows contribute nothing and stay finite
-          dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - delta);
+          dsreg[i] = pack2<T>(dv[0], dv[1]);
         }
-        dsreg[i] = pack2<T>(dv[0], dv[1]);
+        tmem_st16(tdP + lane_sel + c0 + ch * 16, dsreg);
       }
-      tmem_st32(tdP + lane_sel + c0, dsreg);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full);

@@ -222,25 +222,36 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
-      uint32_t sreg[kTile];
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tS + lane_sel + q4 * 32, sreg + q4 * 32);
-      tmem_wait_ld();
-      float* sf = reinterpret_cast<float*>(sreg);
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
                         kt * kTile + kTile <= g.Lk;
-      if (!full) {
-        const int klim = imin(n - kg0, g.Lk - kt * kTile);  // columns >= klim do not exist
+      const int klim = imin(n - kg0, g.Lk - kt * kTile);  // columns >= klim do not exist
+      uint32_t buf[2][32];
+      // ---- pass 1: row maximum.  32 columns at a time, next chunk's TMEM load in flight meanwhile;
+      //      four independent accumulators keep the dependency chains short.
+      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+      tmem_ld32(tS + lane_sel, buf[0]);
 #pragma unroll
-        for (int cidx = 0; cidx < kTile; ++cidx) {
-          const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
-          sf[cidx] = vis ? sf[cidx] : -CUDART_INF_F;
+      for (int ch = 0; ch < 4; ++ch) {
+        tmem_wait_ld();
+        if (ch + 1 < 4) tmem_ld32(tS + lane_sel + (ch + 1) * 32, buf[(ch + 1) & 1]);
+        float* sf = reinterpret_cast<float*>(buf[ch & 1]);
+        if (!full) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int cidx = ch * 32 + i;
+            const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
+            sf[i] = vis ? sf[i] : -CUDART_INF_F;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          mx0 = fmaxf(mx0, sf[i]);
+          mx1 = fmaxf(mx1, sf[i + 1]);
+          mx2 = fmaxf(mx2, sf[i + 2]);
+          mx3 = fmaxf(mx3, sf[i + 3]);
         }
       }
-      float mx = sf[0];
-#pragma unroll
-      for (int cidx = 1; cidx < kTile; ++cidx) mx = fmaxf(mx, sf[cidx]);
-      const float m_tile = mx * c;  // c > 0 (checked by the host)
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // c > 0 (checked by the host)
       const float m_cand = fmaxf(m_used, m_tile);
       if (j == 0) {
         m_used = m_cand;
@@ -262,18 +273,39 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
       }
       const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
-      float lsum = 0.f;
+      // ---- pass 2: P = 2^(S c - m), row sum, 16-bit P written over the S columns already consumed
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      tmem_ld32(tS + lane_sel, buf[0]);
 #pragma unroll
-      for (int cidx = 0; cidx < kTile; ++cidx) {
-        sf[cidx] = ex2(fmaf(sf[cidx], c, -m_safe));
-        lsum += sf[cidx];
+      for (int ch = 0; ch < 4; ++ch) {
+        tmem_wait_ld();
+        if (ch + 1 < 4) tmem_ld32(tS + lane_sel + (ch + 1) * 32, buf[(ch + 1) & 1]);
+        float* sf = reinterpret_cast<float*>(buf[ch & 1]);
+        if (!full) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int cidx = ch * 32 + i;
+            const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
+            sf[i] = vis ? sf[i] : -CUDART_INF_F;
+          }
+        }
+        uint32_t preg[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float p0 = ex2(fmaf(sf[i], c, -m_safe));
+          const float p1 = ex2(fmaf(sf[i + 1], c, -m_safe));
+          const float p2 = ex2(fmaf(sf[i + 2], c, -m_safe));
+          const float p3 = ex2(fmaf(sf[i + 3], c, -m_safe));
+          l0 += p0;
+          l1 += p1;
+          l2 += p2;
+          l3 += p3;
+          preg[i / 2] = pack2<T>(p0, p1);
+          preg[i / 2 + 1] = pack2<T>(p2, p3);
+        }
+        tmem_st16(tS + lane_sel + ch * 16, preg);
       }
-      l += lsum;
-      uint32_t preg[kTile / 2];
-#pragma unroll
-      for (int i = 0; i < kTile / 2; ++i) preg[i] = pack2<T>(sf[2 * i], sf[2 * i + 1]);
-      tmem_st32(tS + lane_sel, preg);
-      tmem_st32(tS + lane_sel + 32, preg + 32);
+      l += (l0 + l1) + (l2 + l3);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full);
