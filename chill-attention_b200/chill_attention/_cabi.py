@@ -33,7 +33,7 @@ BUILTIN_FUNCTOR_IDS = {
 _DTYPES = {torch.float32: CHILL_F32, torch.float16: CHILL_F16, torch.bfloat16: CHILL_BF16}
 
 EXPORTS = (
-    "chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_scratch_bytes", "chill_fwd_uses_tensor_cores",
+    "chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_bwd_scratch_bytes", "chill_fwd_uses_tensor_cores",
     "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits", "chill_read_device_status",
     "chill_abi_version", "chill_status_string", "chill_last_cuda_error",
 )
@@ -93,6 +93,7 @@ def load_library(path: str | None = None) -> C.CDLL:
         lib.chill_fwd.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
         lib.chill_bwd_delta.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
         lib.chill_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
+        lib.chill_bwd_noalloc.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
         lib.chill_bwd_scratch_bytes.argtypes = [C.POINTER(Shape)]
         lib.chill_bwd_scratch_bytes.restype = C.c_size_t
         lib.chill_fwd_uses_tensor_cores.argtypes = [C.POINTER(FwdArgs)]
@@ -102,7 +103,7 @@ def load_library(path: str | None = None) -> C.CDLL:
         lib.chill_status_string.argtypes = [C.c_int]
         lib.chill_status_string.restype = C.c_char_p
         lib.chill_last_cuda_error.restype = C.c_char_p
-        for name in ("chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_fwd_uses_tensor_cores",
+        for name in ("chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_fwd_uses_tensor_cores",
                      "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits",
                      "chill_read_device_status", "chill_abi_version"):
             getattr(lib, name).restype = C.c_int
@@ -169,7 +170,7 @@ def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape) -> BwdAr
     a = BwdArgs()
     a.s = shape
     a.q, a.k, a.v, a.o, a.d_o = (t.data_ptr() for t in (q, k, v, o, do))
-    a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
+    a.lse, a.delta = lse.data_ptr(), (delta.data_ptr() if delta is not None else None)
     a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     (a.q_strides, a.k_strides, a.v_strides, a.o_strides, a.do_strides, a.dq_strides, a.dk_strides,
      a.dv_strides) = (_strides(t, 4) for t in (q, k, v, o, do, dq, dk, dv))
@@ -182,3 +183,13 @@ def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape):
     st = _stream()
     check(lib, lib.chill_bwd_delta(C.byref(a), st), "chill_bwd_delta")
     check(lib, lib.chill_bwd(C.byref(a), st), "chill_bwd")
+
+
+NOALLOC_MAX_ROWS = 1 << 22
+
+
+def backward_noalloc(lib, q, k, v, o, do, lse, dq, dk, dv, shape: Shape):
+    """Backward through ``chill_bwd_noalloc``: the delta scratch lives inside the library
+    (at most NOALLOC_MAX_ROWS = B*H*Lq rows); calls sharing a device must not overlap."""
+    a = backward_args(q, k, v, o, do, lse, None, dq, dk, dv, shape)
+    check(lib, lib.chill_bwd_noalloc(C.byref(a), _stream()), "chill_bwd_noalloc")

@@ -5,6 +5,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "bwd_tc.cuh"
 #include "chill_b200.h"
 #include "fwd_tc.cuh"
@@ -323,6 +325,31 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st) {
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tc launch");
 }
 
+// ------------------------------------------------------------- backward without a scratch argument
+// Library-owned scratch for chill_bwd_noalloc: lives in the device image of this file, one copy per
+// GPU that loads the library.  In host code the name below is only a handle for the runtime; the
+// address the kernels need comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) float g_noalloc_delta[CHILL_NOALLOC_MAX_ROWS];
+
+static int noalloc_scratch(float** out) {
+  constexpr int kMaxDevices = 64;
+  static float* ptrs[kMaxDevices] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return CHILL_E_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_delta);  // resolves against the CURRENT device
+    if (e != cudaSuccess || p == nullptr) return cuda_fail(e, "cudaGetSymbolAddress(noalloc scratch)");
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return CHILL_OK;
+}
+
 template <class M>
 static int traits_of() {
   return (M::kHasKFullRange ? 1 : 0) | (M::kHasQFullRange ? 2 : 0) | (M::kKLimsContinuous ? 4 : 0) |
@@ -387,6 +414,29 @@ int chill_bwd(const chill_bwd_args* a, void* stream) {
   if (bwd_tc_eligible(*a)) return bwd_tc(*a, (cudaStream_t)stream);
   if (a->s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
   return bwd_generic(*a, (cudaStream_t)stream);
+}
+
+int chill_bwd_noalloc(const chill_bwd_args* a, void* stream) {
+  if (a == nullptr) return CHILL_E_INVALID;
+  chill_bwd_args b = *a;  // private copy: the caller's struct is not modified
+  float* scratch = reinterpret_cast<float*>(16);  // placeholder so the pointer check below passes
+  b.delta = scratch;
+  int st = check_bwd(&b, true);
+  if (st != CHILL_OK) return st;
+  const unsigned long long rows = (unsigned long long)b.s.B * (unsigned long long)b.s.H * (unsigned long long)b.s.Lq;
+  if (rows > (unsigned long long)CHILL_NOALLOC_MAX_ROWS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "chill_bwd_noalloc: B*H*Lq = %llu exceeds CHILL_NOALLOC_MAX_ROWS = %u",
+             rows, (unsigned)CHILL_NOALLOC_MAX_ROWS);
+    return CHILL_E_TOO_LARGE;
+  }
+  st = noalloc_scratch(&scratch);
+  if (st != CHILL_OK) return st;
+  b.delta = scratch;
+  st = delta_launch(b, (cudaStream_t)stream);
+  if (st != CHILL_OK) return st;
+  if (bwd_tc_eligible(b)) return bwd_tc(b, (cudaStream_t)stream);
+  if (b.s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
+  return bwd_generic(b, (cudaStream_t)stream);
 }
 
 int chill_mask_tabulate(const chill_mask_desc* m, int32_t n, int32_t tile, uint8_t* dense, int32_t* k_lims,

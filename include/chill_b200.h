@@ -129,6 +129,33 @@ int chill_bwd_delta(const chill_bwd_args* a, void* stream);
  * (enqueue both on the same stream). */
 int chill_bwd(const chill_bwd_args* a, void* stream);
 
+/* chill_bwd_delta + chill_bwd for callers that cannot hand over a scratch buffer.
+ * (No counterpart in the reference: its adapter allocates `delta` with torch.empty on every call.)
+ *
+ * Who needs it: code that runs where device allocation is off limits - a host callback or a
+ * plugin hook invoked while the framework's allocator is locked, a real-time / serving loop with
+ * a frozen memory plan, an embedder that received all its buffers up front and has no allocator
+ * handle to pass down.  Such a caller still owns q, k, v, o, d_o, lse and the three outputs, but
+ * has nowhere to put the B*H*Lq floats of `delta` that the backward kernels exchange.
+ *
+ * This entry point keeps that scratch inside the library: a fixed array in device global memory
+ * (part of the library image, so every GPU that loads the library holds its
+ * CHILL_NOALLOC_MAX_ROWS * 4 bytes = 16 MiB until the process exits).  `a->delta` is ignored and
+ * may be NULL.  The call allocates nothing: no cudaMalloc / cudaFree / stream-ordered allocation
+ * and no allocating library routine.
+ *
+ * Limits and rules:
+ *  - B * H * Lq must not exceed CHILL_NOALLOC_MAX_ROWS, otherwise CHILL_E_TOO_LARGE is returned
+ *    and nothing is launched.
+ *  - The first call on each device looks up the array's device address (one-time set-up with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's contents.
+ *    Nothing in it needs clearing (every row the kernels read is rewritten first by the same
+ *    call), but two calls whose kernels can overlap on the GPU - different streams, no
+ *    dependency between them - race on it.  Serialise them (same stream, or an event). */
+#define CHILL_NOALLOC_MAX_ROWS (1u << 22)
+int chill_bwd_noalloc(const chill_bwd_args* a, void* stream);
+
 /* Bytes of the `delta` scratch buffer chill_bwd_delta / chill_bwd need. */
 size_t chill_bwd_scratch_bytes(const chill_shape* s);
 
