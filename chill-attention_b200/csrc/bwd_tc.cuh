@@ -17,9 +17,17 @@
 //       Reference math: chill_attention/chill_bwd_dq.py:300-394.
 //
 // Roles in both (320 threads): warps 0-7 do the exponentials (thread (w % 4) * 32 + lane owns
-// TMEM lane = tile row; warps 0-3 take columns 0-63, warps 4-7 columns 64-127), warp 8 is the
-// TMA producer and owns the TMEM allocation, warp 9 issues the MMAs.
+// TMEM lane = tile row; warps 0-3 and warps 4-7 split the columns), warp 8 is the TMA producer
+// and owns the TMEM allocation, warp 9 issues the MMAs.
+//
+// Software pipeline: the streamed tile is processed in two halves of 64 positions.  The score
+// accumulators (S/dP) are double-buffered in TMEM (2 x 64 columns each), and the MMA issuer runs
+// one half ahead: while the compute warps turn half u into P/dS, the tensor cores already work
+// on the scores of half u+1, and the accumulating GEMMs of half u follow as soon as its P/dS
+// are in TMEM.
 #pragma once
+#include <type_traits>
+
 #include "fwd_tc.cuh"
 #include "generic.cuh"
 #include "tc_common.cuh"
@@ -52,7 +60,7 @@ struct BwdSmem {
   static constexpr int kRing = kFixB + kTileBytes;     // per stage: [Q | dO] (dkdv) or [K | V] (dq)
   static constexpr int kRows = kRing + kStages * 2 * kTileBytes;  // per compute warp: lse[64], delta[64] floats
   static constexpr int kBars = kRows + 8 * 2 * 64 * 4;
-  static constexpr int kNumBars = 4 + 2 * kStages;
+  static constexpr int kNumBars = 6 + 2 * kStages;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;
@@ -139,8 +147,9 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t sK = base + L::kFixA, sV = base + L::kFixB, sRing = base + L::kRing;
   float* rows_s = reinterpret_cast<float*>(gen_base + L::kRows);  // [warp][0: lse, 1: delta][64]
   const uint32_t bars = base + L::kBars;
-  const uint32_t bar_kv_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_acc_full = bars + 24;
-  const uint32_t bar_ring_full = bars + 32, bar_ring_empty = bar_ring_full + 8 * L::kStages;
+  // s_full / p_full: one barrier per score buffer (index = half & 1)
+  const uint32_t bar_kv_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_p_full = bars + 32;
+  const uint32_t bar_ring_full = bars + 48, bar_ring_empty = bar_ring_full + 8 * L::kStages;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
   const Guard guard{p.status, abort_flag};
@@ -148,9 +157,11 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_kv_full, 1);
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, kBwdComputeThreads);
     mbar_init(bar_acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_p_full + 8 * i, kBwdComputeThreads / 32);
+    }
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(bar_ring_full + 8 * s, 1);
       mbar_init(bar_ring_empty + 8 * s, 1);
@@ -201,114 +212,135 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp == 9) {
     // ----------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, 64, false, false);
       constexpr uint32_t idesc_acc = make_idesc<T>(kTile, D, false, true);
+      const int n_half = 2 * n_it;
       bool ok = mbar_wait(bar_kv_full, 0, guard, kStBwdMma);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it % L::kStages;
-        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+      // S^T / dP^T of half u (64 queries) into score buffer u & 1
+      auto issue_scores = [&](int u) -> bool {
+        const int it = u >> 1, hf = u & 1, s = it % L::kStages;
         const uint32_t sQ = sRing + s * 2 * L::kTileBytes, sdO = sQ + L::kTileBytes;
-        ok = mbar_wait(bar_ring_full + 8 * s, ph, guard, kStBwdMma);
-        if (!ok) break;
-        tc_fence_after();
+        if (hf == 0) {
+          if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)(it / L::kStages) & 1u, guard, kStBwdMma)) return false;
+          tc_fence_after();
+        }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {  // S^T = K Q^T
+        for (int kk = 0; kk < D / 16; ++kk) {  // S^T = K Q^T   (B = 64 query rows of the Q tile)
           const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tSt, smem_desc_sw128(sK + off, 16, 1024), smem_desc_sw128(sQ + off, 16, 1024), idesc_s, kk > 0);
+          mma_ss(tSt + hf * 64, smem_desc_sw128(sK + off, 16, 1024), smem_desc_sw128(sQ + off + hf * 8192, 16, 1024),
+                 idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {  // dP^T = V dO^T
           const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tdPt, smem_desc_sw128(sV + off, 16, 1024), smem_desc_sw128(sdO + off, 16, 1024), idesc_s, kk > 0);
+          mma_ss(tdPt + hf * 64, smem_desc_sw128(sV + off, 16, 1024), smem_desc_sw128(sdO + off + hf * 8192, 16, 1024),
+                 idesc_s, kk > 0);
         }
-        mma_commit(bar_s_full);
-        ok = mbar_wait(bar_p_full, (uint32_t)it & 1u, guard, kStBwdMma);
+        mma_commit(bar_s_full + 8 * hf);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int u = 0; u < n_half && ok; ++u) {
+        const int it = u >> 1, hf = u & 1, s = it % L::kStages;
+        const uint32_t sQ = sRing + s * 2 * L::kTileBytes, sdO = sQ + L::kTileBytes;
+        if (u + 1 < n_half) {
+          ok = issue_scores(u + 1);  // tensor cores stay busy while half u is exponentiated
+          if (!ok) break;
+        }
+        ok = mbar_wait(bar_p_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStBwdMma);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {  // dV += P^T dO ; dK += dS^T Q   (16 queries per step)
-          const uint32_t acol = (kk / 4) * 64 + (kk % 4) * 8;
-          mma_ts(tdV, tSt + acol, smem_desc_sw128(sdO + kk * 2048, kChunkBytes, 1024), idesc_acc, (it > 0 || kk > 0));
-          mma_ts(tdK, tdPt + acol, smem_desc_sw128(sQ + kk * 2048, kChunkBytes, 1024), idesc_acc, (it > 0 || kk > 0));
+        for (int kk = 0; kk < 4; ++kk) {  // dV += P^T dO ; dK += dS^T Q   (16 of the half's 64 queries per step)
+          const uint32_t acol = hf * 64 + (kk / 2) * 32 + (kk % 2) * 8;
+          const uint32_t boff = (hf * 4 + kk) * 2048;
+          mma_ts(tdV, tSt + acol, smem_desc_sw128(sdO + boff, kChunkBytes, 1024), idesc_acc, (u > 0 || kk > 0));
+          mma_ts(tdK, tdPt + acol, smem_desc_sw128(sQ + boff, kChunkBytes, 1024), idesc_acc, (u > 0 || kk > 0));
         }
-        mma_commit(bar_ring_empty + 8 * s);
+        if (hf == 1) mma_commit(bar_ring_empty + 8 * s);
       }
       if (ok) mma_commit(bar_acc_full);
     }
   } else {
     // ------------------------------------------------------------------- compute warps
-    const int wg = warp >> 2;                       // column half
+    const int wg = warp >> 2;                       // which 32 columns of a half
     const int r = (warp & 3) * 32 + lane;           // key row inside the tile == TMEM lane
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const int c0 = wg * 64;
+    const int cw0 = wg * 32;
     const int kg = kg0 + r;
     const bool key_ok = kg < n && kb + r < g.Lk;
     const float c = g.scale * kLog2e;
     const int t = threadIdx.x;  // 0..255
+    float* slot = rows_s + warp * 128;  // warp-private: [0,32) LSE, [64,96) delta of this warp's columns
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
+    const int n_half = 2 * n_it;
+    for (int u = 0; u < n_half; ++u) {
+      const int it = u >> 1, hf = u & 1;
       const int h = hk * G + it / n_qt;
       const int qi = qt_lo + it % n_qt;
       const int qg0 = qi * kTile + g.q_off;
-      // LSE and delta of this warp's 64 query columns, staged in a warp-private slot (no CTA barrier)
-      float* slot = rows_s + warp * 128;
+      const int cbase = hf * 64 + cw0;  // first of this warp's 32 query columns inside the tile
       __syncwarp();
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int col = c0 + e * 32 + lane, qrow = qi * kTile + col;
+      {
+        const int qrow = qi * kTile + cbase + lane;
         float lv = 0.f, dl = 0.f;
         if (qrow < g.Lq) {
           lv = p.lse[b * p.lse_sb + h * p.lse_sh + qrow * p.lse_sl];
           if (lv == -CUDART_INF_F) lv = 0.f;
           dl = p.delta[((long long)b * g.H + h) * g.Lq + qrow];
         }
-        slot[e * 32 + lane] = lv;
-        slot[64 + e * 32 + lane] = dl;
+        slot[lane] = lv;
+        slot[64 + lane] = dl;
       }
       __syncwarp();
-      ok = mbar_wait(bar_s_full, (uint32_t)it & 1u, guard, kStBwdCompute);
+      ok = mbar_wait(bar_s_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStBwdCompute);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
       const bool full = M::kHasQFullRange && qg0 >= full_lo && qg0 + kTile <= full_hi && qg0 + kTile <= n &&
                         qi * kTile + kTile <= g.Lq && kg0 + kTile <= n && kb + kTile <= g.Lk;
       const int qlim = imin(n - qg0, g.Lq - qi * kTile);
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {  // 32 query columns at a time
-        uint32_t sreg[32], dpreg[32], preg[16], dsreg[16];
-        tmem_ld32(tSt + lane_sel + c0 + ch * 32, sreg);
-        tmem_ld32(tdPt + lane_sel + c0 + ch * 32, dpreg);
-        tmem_wait_ld();
+      uint32_t sreg[32], dpreg[32], preg[16], dsreg[16];
+      tmem_ld32(tSt + lane_sel + cbase, sreg);
+      tmem_ld32(tdPt + lane_sel + cbase, dpreg);
+      tmem_wait_ld();
+      auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
+        constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float pv[2], dv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int cw = ch * 32 + 2 * i + e;  // column inside this warp's 64
-            float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -slot[cw]));
-            if (!full) {
-              const bool vis = key_ok && c0 + cw < qlim && M::mask(qg0 + c0 + cw, kg, n, g.margs);
+            const int cw = 2 * i + e;
+            float pe = ex2(fmaf(__uint_as_float(sreg[cw]), c, -slot[cw]));
+            if (kMasked) {
+              const bool vis = key_ok && cbase + cw < qlim && M::mask(qg0 + cbase + cw, kg, n, g.margs);
               pe = vis ? pe : 0.f;
             }
             pv[e] = pe;
-            dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - slot[64 + cw]);
+            dv[e] = pe * (__uint_as_float(dpreg[cw]) - slot[64 + cw]);
           }
           preg[i] = pack2<T>(pv[0], pv[1]);
           dsreg[i] = pack2<T>(dv[0], dv[1]);
         }
-        // 16-bit P^T / dS^T over the fp32 columns just consumed (own column range only)
-        tmem_st16(tSt + lane_sel + c0 + ch * 16, preg);
-        tmem_st16(tdPt + lane_sel + c0 + ch * 16, dsreg);
-      }
+      };
+      if (full) body(std::false_type{});
+      else body(std::true_type{});
+      // 16-bit P^T / dS^T over the fp32 columns this warp just consumed
+      tmem_st16(tSt + lane_sel + cbase, preg);
+      tmem_st16(tdPt + lane_sel + cbase, dsreg);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p_full + 8 * hf);  // one arrival per compute warp
     }
 
     // ---- epilogue: warps 0-3 store dV, warps 4-7 store dK * sm_scale (staging = ring stage 0)
     if (ok) ok = mbar_wait(bar_acc_full, 0, guard, kStBwdEpilogue);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
+    const int c0 = 0;
+    (void)c0;
     uint8_t* stage = gen_base + L::kRing + wg * L::kTileBytes;
     const uint32_t tacc = wg == 0 ? tdV : tdK;
     const float mul = wg == 0 ? 1.f : g.scale;
@@ -380,8 +412,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t sQ = base + L::kFixA, sdO = base + L::kFixB, sRing = base + L::kRing;
   const uint32_t bars = base + L::kBars;
-  const uint32_t bar_q_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_acc_full = bars + 24;
-  const uint32_t bar_ring_full = bars + 32, bar_ring_empty = bar_ring_full + 8 * L::kStages;
+  const uint32_t bar_q_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_p_full = bars + 32;
+  const uint32_t bar_ring_full = bars + 48, bar_ring_empty = bar_ring_full + 8 * L::kStages;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
   const Guard guard{p.status, abort_flag};
@@ -389,9 +421,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_q_full, 1);
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, kBwdComputeThreads);
     mbar_init(bar_acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_p_full + 8 * i, kBwdComputeThreads / 32);
+    }
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(bar_ring_full + 8 * s, 1);
       mbar_init(bar_ring_empty + 8 * s, 1);
@@ -439,36 +473,51 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 9) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, 64, false, false);
       constexpr uint32_t idesc_acc = make_idesc<T>(kTile, D, false, true);
+      const int n_half = 2 * n_it;
       bool ok = mbar_wait(bar_q_full, 0, guard, kStDqMma);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it % L::kStages;
-        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+      // S / dP of half u (64 keys) into score buffer u & 1
+      auto issue_scores = [&](int u) -> bool {
+        const int it = u >> 1, hf = u & 1, s = it % L::kStages;
         const uint32_t sK = sRing + s * 2 * L::kTileBytes, sV = sK + L::kTileBytes;
-        ok = mbar_wait(bar_ring_full + 8 * s, ph, guard, kStDqMma);
-        if (!ok) break;
-        tc_fence_after();
+        if (hf == 0) {
+          if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)(it / L::kStages) & 1u, guard, kStDqMma)) return false;
+          tc_fence_after();
+        }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {  // S = Q K^T
+        for (int kk = 0; kk < D / 16; ++kk) {  // S = Q K^T   (B = 64 key rows of the K tile)
           const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tS, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_s, kk > 0);
+          mma_ss(tS + hf * 64, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off + hf * 8192, 16, 1024),
+                 idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {  // dP = dO V^T
           const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tdP, smem_desc_sw128(sdO + off, 16, 1024), smem_desc_sw128(sV + off, 16, 1024), idesc_s, kk > 0);
+          mma_ss(tdP + hf * 64, smem_desc_sw128(sdO + off, 16, 1024), smem_desc_sw128(sV + off + hf * 8192, 16, 1024),
+                 idesc_s, kk > 0);
         }
-        mma_commit(bar_s_full);
-        ok = mbar_wait(bar_p_full, (uint32_t)it & 1u, guard, kStDqMma);
+        mma_commit(bar_s_full + 8 * hf);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int u = 0; u < n_half && ok; ++u) {
+        const int it = u >> 1, hf = u & 1, s = it % L::kStages;
+        const uint32_t sK = sRing + s * 2 * L::kTileBytes;
+        if (u + 1 < n_half) {
+          ok = issue_scores(u + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(bar_p_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStDqMma);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {  // dQ += dS K   (16 keys per step)
-          const uint32_t acol = (kk / 4) * 64 + (kk % 4) * 8;
-          mma_ts(tdQ, tdP + acol, smem_desc_sw128(sK + kk * 2048, kChunkBytes, 1024), idesc_acc, (it > 0 || kk > 0));
+        for (int kk = 0; kk < 4; ++kk) {  // dQ += dS K   (16 of the half's 64 keys per step)
+          const uint32_t acol = hf * 64 + (kk / 2) * 32 + (kk % 2) * 8;
+          mma_ts(tdQ, tdP + acol, smem_desc_sw128(sK + (hf * 4 + kk) * 2048, kChunkBytes, 1024), idesc_acc,
+                 (u > 0 || kk > 0));
         }
-        mma_commit(bar_ring_empty + 8 * s);
+        if (hf == 1) mma_commit(bar_ring_empty + 8 * s);
       }
       if (ok) mma_commit(bar_acc_full);
     }
@@ -476,7 +525,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;  // query row inside the tile
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const int c0 = wg * 64;
+    const int cw0 = wg * 32;
     const int qg = qg0 + r;
     const bool row_ok = qg < n && qb + r < g.Lq;
     const float c = g.scale * kLog2e;
@@ -486,44 +535,50 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lse == -CUDART_INF_F) lse = 0.f;
       delta = p.delta[((long long)b * g.H + h) * g.Lq + qb + r];
     }
+    if (!row_ok) lse = CUDART_INF_F;  // padded query rows: 2^(x - inf) = 0, so they contribute nothing and stay finite
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
+    const int n_half = 2 * n_it;
+    for (int u = 0; u < n_half; ++u) {
+      const int it = u >> 1, hf = u & 1;
       const int kt = kt_lo + it;
       const int kg0 = kt * kTile + g.k_off;
-      ok = mbar_wait(bar_s_full, (uint32_t)it & 1u, guard, kStDqCompute);
+      const int cbase = hf * 64 + cw0;  // first of this warp's 32 key columns inside the tile
+      ok = mbar_wait(bar_s_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStDqCompute);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
                         kt * kTile + kTile <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * kTile);
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {  // 32 key columns at a time
-        uint32_t sreg[32], dpreg[32], dsreg[16];
-        tmem_ld32(tS + lane_sel + c0 + ch * 32, sreg);
-        tmem_ld32(tdP + lane_sel + c0 + ch * 32, dpreg);
-        tmem_wait_ld();
+      uint32_t sreg[32], dpreg[32], dsreg[16];
+      tmem_ld32(tS + lane_sel + cbase, sreg);
+      tmem_ld32(tdP + lane_sel + cbase, dpreg);
+      tmem_wait_ld();
+      auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
+        constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float dv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int col = c0 + ch * 32 + 2 * i + e;
-            float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -lse));
-            if (!full) {
+            const int col = cbase + 2 * i + e;
+            float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -lse));  // lse = +inf on padded rows: pe = 0
+            if (kMasked) {
               const bool vis = col < klim && M::mask(qg, kg0 + col, n, g.margs);
               pe = vis ? pe : 0.f;
             }
-            pe = row_ok ? pe : 0.f;  // padded query rows contribute nothing and stay finite
             dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - delta);
           }
           dsreg[i] = pack2<T>(dv[0], dv[1]);
         }
-        tmem_st16(tdP + lane_sel + c0 + ch * 16, dsreg);
-      }
+      };
+      if (full) body(std::false_type{});
+      else body(std::true_type{});
+      tmem_st16(tdP + lane_sel + cbase, dsreg);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p_full + 8 * hf);  // one arrival per compute warp
     }
 
     // ---- epilogue: dQ * sm_scale; warps 0-3 take channels [0, D/2), warps 4-7 the rest

@@ -19,6 +19,8 @@
 // online softmax, LSE = m + log2 l); the segment split is replaced by a per-tile "full tile"
 // test derived from the functor's k_full_range_for_q.
 #pragma once
+#include <type_traits>
+
 #include "generic.cuh"
 #include "tc_common.cuh"
 
@@ -118,7 +120,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     *abort_flag = 0;
     mbar_init(bar_q_full, 1);
     mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, 128);
+    mbar_init(bar_p_full, 4);
     mbar_init(bar_o_full, 1);
     for (int s = 0; s < NSTAGE; ++s) {
       mbar_init(bar_k_full + 8 * s, 1);
@@ -225,90 +227,98 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
                         kt * kTile + kTile <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * kTile);  // columns >= klim do not exist
+      // The tile body exists twice - with and without mask evaluation - so that full tiles run a
+      // predicate-free loop (the compiler would otherwise if-convert the mask into every iteration).
+      auto tile_body = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
       uint32_t buf[2][32];
-      // ---- pass 1: row maximum.  32 columns at a time, next chunk's TMEM load in flight meanwhile;
-      //      four independent accumulators keep the dependency chains short.
-      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
-      tmem_ld32(tS + lane_sel, buf[0]);
+        // ---- pass 1: row maximum.  32 columns at a time, next chunk's TMEM load in flight meanwhile;
+        //      four independent accumulators keep the dependency chains short.
+        float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+        tmem_ld32(tS + lane_sel, buf[0]);
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        tmem_wait_ld();
-        if (ch + 1 < 4) tmem_ld32(tS + lane_sel + (ch + 1) * 32, buf[(ch + 1) & 1]);
-        float* sf = reinterpret_cast<float*>(buf[ch & 1]);
-        if (!full) {
+        for (int ch = 0; ch < 4; ++ch) {
+          tmem_wait_ld();
+          if (ch + 1 < 4) tmem_ld32(tS + lane_sel + (ch + 1) * 32, buf[(ch + 1) & 1]);
+          float* sf = reinterpret_cast<float*>(buf[ch & 1]);
+          if (kMasked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int cidx = ch * 32 + i;
-            const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
-            sf[i] = vis ? sf[i] : -CUDART_INF_F;
+            for (int i = 0; i < 32; ++i) {
+              const int cidx = ch * 32 + i;
+              const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
+              sf[i] = vis ? sf[i] : -CUDART_INF_F;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, sf[i]);
+            mx1 = fmaxf(mx1, sf[i + 1]);
+            mx2 = fmaxf(mx2, sf[i + 2]);
+            mx3 = fmaxf(mx3, sf[i + 3]);
           }
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          mx0 = fmaxf(mx0, sf[i]);
-          mx1 = fmaxf(mx1, sf[i + 1]);
-          mx2 = fmaxf(mx2, sf[i + 2]);
-          mx3 = fmaxf(mx3, sf[i + 3]);
-        }
-      }
-      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // c > 0 (checked by the host)
-      const float m_cand = fmaxf(m_used, m_tile);
-      if (j == 0) {
-        m_used = m_cand;
-      } else {
-        const bool need = (m_cand - m_used) > kRescaleThreshold;  // false when both are -inf
-        if (__any_sync(0xffffffffu, need)) {
-          const float alpha = (m_cand == -CUDART_INF_F) ? 1.f : ex2(m_used - m_cand);
-          l *= alpha;
+        const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // c > 0 (checked by the host)
+        const float m_cand = fmaxf(m_used, m_tile);
+        if (j == 0) {
           m_used = m_cand;
+        } else {
+          const bool need = (m_cand - m_used) > kRescaleThreshold;  // false when both are -inf
+          if (__any_sync(0xffffffffu, need)) {
+            const float alpha = (m_cand == -CUDART_INF_F) ? 1.f : ex2(m_used - m_cand);
+            l *= alpha;
+            m_used = m_cand;
 #pragma unroll
-          for (int q4 = 0; q4 < D / 32; ++q4) {
-            uint32_t oreg[32];
-            tmem_ld32(tO + lane_sel + q4 * 32, oreg);
-            tmem_wait_ld();
+            for (int q4 = 0; q4 < D / 32; ++q4) {
+              uint32_t oreg[32];
+              tmem_ld32(tO + lane_sel + q4 * 32, oreg);
+              tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-            tmem_st32(tO + lane_sel + q4 * 32, oreg);
+              for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+              tmem_st32(tO + lane_sel + q4 * 32, oreg);
+            }
           }
         }
-      }
-      const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
-      // ---- pass 2: P = 2^(S c - m), row sum, 16-bit P written over the S columns already consumed
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-      tmem_ld32(tS + lane_sel, buf[0]);
+        const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
+        // ---- pass 2: P = 2^(S c - m), row sum, 16-bit P written over the S columns already consumed
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        tmem_ld32(tS + lane_sel, buf[0]);
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        tmem_wait_ld();
-        if (ch + 1 < 4) tmem_ld32(tS + lane_sel + (ch + 1) * 32, buf[(ch + 1) & 1]);
-        float* sf = reinterpret_cast<float*>(buf[ch & 1]);
-        if (!full) {
+        for (int ch = 0; ch < 4; ++ch) {
+          tmem_wait_ld();
+          if (ch + 1 < 4) tmem_ld32(tS + lane_sel + (ch + 1) * 32, buf[(ch + 1) & 1]);
+          float* sf = reinterpret_cast<float*>(buf[ch & 1]);
+          if (kMasked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int cidx = ch * 32 + i;
-            const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
-            sf[i] = vis ? sf[i] : -CUDART_INF_F;
+            for (int i = 0; i < 32; ++i) {
+              const int cidx = ch * 32 + i;
+              const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
+              sf[i] = vis ? sf[i] : -CUDART_INF_F;
+            }
           }
-        }
-        uint32_t preg[16];
+          uint32_t preg[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float p0 = ex2(fmaf(sf[i], c, -m_safe));
-          const float p1 = ex2(fmaf(sf[i + 1], c, -m_safe));
-          const float p2 = ex2(fmaf(sf[i + 2], c, -m_safe));
-          const float p3 = ex2(fmaf(sf[i + 3], c, -m_safe));
-          l0 += p0;
-          l1 += p1;
-          l2 += p2;
-          l3 += p3;
-          preg[i / 2] = pack2<T>(p0, p1);
-          preg[i / 2 + 1] = pack2<T>(p2, p3);
+          for (int i = 0; i < 32; i += 4) {
+            const float p0 = ex2(fmaf(sf[i], c, -m_safe));
+            const float p1 = ex2(fmaf(sf[i + 1], c, -m_safe));
+            const float p2 = ex2(fmaf(sf[i + 2], c, -m_safe));
+            const float p3 = ex2(fmaf(sf[i + 3], c, -m_safe));
+            l0 += p0;
+            l1 += p1;
+            l2 += p2;
+            l3 += p3;
+            preg[i / 2] = pack2<T>(p0, p1);
+            preg[i / 2 + 1] = pack2<T>(p2, p3);
+          }
+          tmem_st16(tS + lane_sel + ch * 16, preg);
         }
-        tmem_st16(tS + lane_sel + ch * 16, preg);
-      }
-      l += (l0 + l1) + (l2 + l3);
+        l += (l0 + l1) + (l2 + l3);
+      };
+      if (full) tile_body(std::false_type{});
+      else tile_body(std::true_type{});
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p_full);  // one arrival per softmax warp
     }
 
     // ---- epilogue: O / l -> 16-bit -> swizzled shared memory (Q's buffer) -> TMA store
