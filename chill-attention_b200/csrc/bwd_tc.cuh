@@ -289,8 +289,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (lv == -CUDART_INF_F) lv = 0.f;
           dl = p.delta[((long long)b * g.H + h) * g.Lq + qrow];
         }
-        slot[lane] = lv;
-        slot[64 + lane] = dl;
+        slot[lane] = -lv;  // negated: they enter the packed FMA / ADD as addends
+        slot[64 + lane] = -dl;
       }
       __syncwarp();
       ok = mbar_wait(bar_s_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStBwdCompute);
@@ -304,24 +304,34 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_ld32(tSt + lane_sel + cbase, sreg);
       tmem_ld32(tdPt + lane_sel + cbase, dpreg);
       tmem_wait_ld();
+      // Packed fp32 pairs throughout; the slot holds -LSE and -delta so both enter as FMA / ADD addends.
+      const uint64_t c2 = pk2(c, c);
       auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
         constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int cw = 2 * i + e;
-            float pe = ex2(fmaf(__uint_as_float(sreg[cw]), c, -slot[cw]));
-            if (kMasked) {
-              const bool vis = key_ok && cbase + cw < qlim && M::mask(qg0 + cbase + cw, kg, n, g.margs);
-              pe = vis ? pe : 0.f;
-            }
-            pv[e] = pe;
-            dv[e] = pe * (__uint_as_float(dpreg[cw]) - slot[64 + cw]);
+        for (int j = 0; j < 8; ++j) {  // four query columns per step
+          const float4 nl4 = reinterpret_cast<const float4*>(slot)[j];
+          const float4 nd4 = reinterpret_cast<const float4*>(slot + 64)[j];
+          float p0, p1, p2, p3, d0, d1, d2, d3;
+          upk2(ffma2(pk2u(sreg[4 * j], sreg[4 * j + 1]), c2, pk2(nl4.x, nl4.y)), p0, p1);
+          upk2(ffma2(pk2u(sreg[4 * j + 2], sreg[4 * j + 3]), c2, pk2(nl4.z, nl4.w)), p2, p3);
+          p0 = ex2(p0);
+          p1 = ex2(p1);
+          p2 = ex2(p2);
+          p3 = ex2(p3);
+          if (kMasked) {
+            const int cq = cbase + 4 * j;
+            p0 = (key_ok && cq < qlim && M::mask(qg0 + cq, kg, n, g.margs)) ? p0 : 0.f;
+            p1 = (key_ok && cq + 1 < qlim && M::mask(qg0 + cq + 1, kg, n, g.margs)) ? p1 : 0.f;
+            p2 = (key_ok && cq + 2 < qlim && M::mask(qg0 + cq + 2, kg, n, g.margs)) ? p2 : 0.f;
+            p3 = (key_ok && cq + 3 < qlim && M::mask(qg0 + cq + 3, kg, n, g.margs)) ? p3 : 0.f;
           }
-          preg[i] = pack2<T>(pv[0], pv[1]);
-          dsreg[i] = pack2<T>(dv[0], dv[1]);
+          upk2(fmul2(pk2(p0, p1), fadd2(pk2u(dpreg[4 * j], dpreg[4 * j + 1]), pk2(nd4.x, nd4.y))), d0, d1);
+          upk2(fmul2(pk2(p2, p3), fadd2(pk2u(dpreg[4 * j + 2], dpreg[4 * j + 3]), pk2(nd4.z, nd4.w))), d2, d3);
+          preg[2 * j] = pack2<T>(p0, p1);
+          preg[2 * j + 1] = pack2<T>(p2, p3);
+          dsreg[2 * j] = pack2<T>(d0, d1);
+          dsreg[2 * j + 1] = pack2<T>(d2, d3);
         }
       };
       if (full) body(std::false_type{});
@@ -554,22 +564,22 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld32(tS + lane_sel + cbase, sreg);
       tmem_ld32(tdP + lane_sel + cbase, dpreg);
       tmem_wait_ld();
+      const uint64_t c2 = pk2(c, c), nl2 = pk2(-lse, -lse), nd2 = pk2(-delta, -delta);
       auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
         constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = cbase + 2 * i + e;
-            float pe = ex2(fmaf(__uint_as_float(sreg[2 * i + e]), c, -lse));  // lse = +inf on padded rows: pe = 0
-            if (kMasked) {
-              const bool vis = col < klim && M::mask(qg, kg0 + col, n, g.margs);
-              pe = vis ? pe : 0.f;
-            }
-            dv[e] = pe * (__uint_as_float(dpreg[2 * i + e]) - delta);
+        for (int i = 0; i < 16; ++i) {  // packed fp32 pairs; lse = +inf on padded rows gives p = 0
+          float p0, p1, d0, d1;
+          upk2(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nl2), p0, p1);
+          p0 = ex2(p0);
+          p1 = ex2(p1);
+          if (kMasked) {
+            const int col = cbase + 2 * i;
+            p0 = (col < klim && M::mask(qg, kg0 + col, n, g.margs)) ? p0 : 0.f;
+            p1 = (col + 1 < klim && M::mask(qg, kg0 + col + 1, n, g.margs)) ? p1 : 0.f;
           }
-          dsreg[i] = pack2<T>(dv[0], dv[1]);
+          upk2(fmul2(pk2(p0, p1), fadd2(pk2u(dpreg[2 * i], dpreg[2 * i + 1]), nd2)), d0, d1);
+          dsreg[i] = pack2<T>(d0, d1);
         }
       };
       if (full) body(std::false_type{});

@@ -28,7 +28,9 @@ namespace chill {
 namespace tc {
 
 constexpr int kTile = 128;          // query rows per CTA and keys per tile
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 256;      // warps 0-3 softmax, 4 TMA producer, 5 MMA issuer, 6-7 idle
+constexpr int kFwdSoftmaxRegs = 200;  // per-thread register budget after setmaxnreg (2 CTAs/SM:
+constexpr int kFwdOtherRegs = 56;     //   2 * 128 * (200 + 56) = 65536)
 constexpr int kTmemColsFwd = 256;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
@@ -143,6 +145,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t tO = tmem + kTile;    // O columns
 
   if (warp == 4) {
+    reg_dealloc<kFwdOtherRegs>();
     // ------------------------------------------------------------------- TMA producer
     if (lane == 0 && n_tiles > 0) {
       prefetch_tmap(&tmQ);
@@ -173,6 +176,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
     }
   } else if (warp == 5) {
+    reg_dealloc<kFwdOtherRegs>();
     // --------------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
@@ -209,7 +213,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       if (ok) mma_commit(bar_o_full);
     }
+  } else if (warp >= 6) {
+    reg_dealloc<kFwdOtherRegs>();  // idle warps of the second warpgroup only give their registers back
   } else {
+    reg_alloc<kFwdSoftmaxRegs>();
     // --------------------------------------------------------- softmax + epilogue warps
     const int r = warp * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
@@ -227,94 +234,75 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
                         kt * kTile + kTile <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * kTile);  // columns >= klim do not exist
-      // The tile body exists twice - with and without mask evaluation - so that full tiles run a
-      // predicate-free loop (the compiler would otherwise if-convert the mask into every iteration).
-      auto tile_body = [&](auto masked_tag) {
-        constexpr bool kMasked = decltype(masked_tag)::value;
-      uint32_t buf[2][32];
-        // ---- pass 1: row maximum.  32 columns at a time, next chunk's TMEM load in flight meanwhile;
-        //      four independent accumulators keep the dependency chains short.
-        float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
-        tmem_ld32(tS + lane_sel, buf[0]);
+      // One pass over the row: all 128 scores of this thread's row come into registers, the maximum
+      // is taken with 3-input max on four independent chains, and exponentials, row sum and the
+      // 16-bit packing run on pairs (packed fp32 FMA / ADD).  Full tiles skip the mask arithmetic
+      // (separate copy of the body, so nothing is if-converted into the fast path).
+      uint32_t sreg[kTile];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_wait_ld();
-          if (ch + 1 < 4) tmem_ld32(tS + lane_sel + (ch + 1) * 32, buf[(ch + 1) & 1]);
-          float* sf = reinterpret_cast<float*>(buf[ch & 1]);
-          if (kMasked) {
+      for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tS + lane_sel + q4 * 32, sreg + q4 * 32);
+      tmem_wait_ld();
+      if (!full) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int cidx = ch * 32 + i;
-              const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
-              sf[i] = vis ? sf[i] : -CUDART_INF_F;
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, sf[i]);
-            mx1 = fmaxf(mx1, sf[i + 1]);
-            mx2 = fmaxf(mx2, sf[i + 2]);
-            mx3 = fmaxf(mx3, sf[i + 3]);
-          }
+        for (int cidx = 0; cidx < kTile; ++cidx) {
+          const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
+          sreg[cidx] = vis ? sreg[cidx] : 0xff800000u;  // -inf
         }
-        const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // c > 0 (checked by the host)
-        const float m_cand = fmaxf(m_used, m_tile);
-        if (j == 0) {
+      }
+      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+#pragma unroll
+      for (int i = 0; i < kTile; i += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(sreg[i + 4]), __uint_as_float(sreg[i + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(sreg[i + 6]), __uint_as_float(sreg[i + 7]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // c > 0 (checked by the host)
+      const float m_cand = fmaxf(m_used, m_tile);
+      if (j == 0) {
+        m_used = m_cand;
+      } else {
+        const bool need = (m_cand - m_used) > kRescaleThreshold;  // false when both are -inf
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = (m_cand == -CUDART_INF_F) ? 1.f : ex2(m_used - m_cand);
+          l *= alpha;
           m_used = m_cand;
-        } else {
-          const bool need = (m_cand - m_used) > kRescaleThreshold;  // false when both are -inf
-          if (__any_sync(0xffffffffu, need)) {
-            const float alpha = (m_cand == -CUDART_INF_F) ? 1.f : ex2(m_used - m_cand);
-            l *= alpha;
-            m_used = m_cand;
+#pragma unroll 1
+          for (int q4 = 0; q4 < D / 16; ++q4) {
+            uint32_t oreg[16];
+            tmem_ld16(tO + lane_sel + q4 * 16, oreg);
+            tmem_wait_ld();
 #pragma unroll
-            for (int q4 = 0; q4 < D / 32; ++q4) {
-              uint32_t oreg[32];
-              tmem_ld32(tO + lane_sel + q4 * 32, oreg);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-              tmem_st32(tO + lane_sel + q4 * 32, oreg);
-            }
+            for (int i = 0; i < 16; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+            tmem_st16(tO + lane_sel + q4 * 16, oreg);
           }
         }
-        const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
-        // ---- pass 2: P = 2^(S c - m), row sum, 16-bit P written over the S columns already consumed
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-        tmem_ld32(tS + lane_sel, buf[0]);
+      }
+      const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
+      const uint64_t c2 = pk2(c, c), nm2 = pk2(-m_safe, -m_safe);
+      uint64_t l0 = 0ull, l1 = 0ull;  // two packed partial row sums (+0.0f, +0.0f)
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_wait_ld();
-          if (ch + 1 < 4) tmem_ld32(tS + lane_sel + (ch + 1) * 32, buf[(ch + 1) & 1]);
-          float* sf = reinterpret_cast<float*>(buf[ch & 1]);
-          if (kMasked) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int cidx = ch * 32 + i;
-              const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
-              sf[i] = vis ? sf[i] : -CUDART_INF_F;
-            }
-          }
-          uint32_t preg[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float p0 = ex2(fmaf(sf[i], c, -m_safe));
-            const float p1 = ex2(fmaf(sf[i + 1], c, -m_safe));
-            const float p2 = ex2(fmaf(sf[i + 2], c, -m_safe));
-            const float p3 = ex2(fmaf(sf[i + 3], c, -m_safe));
-            l0 += p0;
-            l1 += p1;
-            l2 += p2;
-            l3 += p3;
-            preg[i / 2] = pack2<T>(p0, p1);
-            preg[i / 2 + 1] = pack2<T>(p2, p3);
-          }
-          tmem_st16(tS + lane_sel + ch * 16, preg);
-        }
-        l += (l0 + l1) + (l2 + l3);
-      };
-      if (full) tile_body(std::false_type{});
-      else tile_body(std::true_type{});
+      for (int i = 0; i < kTile / 2; i += 2) {
+        float p0, p1, p2, p3;
+        upk2(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nm2), p0, p1);
+        upk2(ffma2(pk2u(sreg[2 * i + 2], sreg[2 * i + 3]), c2, nm2), p2, p3);
+        p0 = ex2(p0);
+        p1 = ex2(p1);
+        p2 = ex2(p2);
+        p3 = ex2(p3);
+        l0 = fadd2(l0, pk2(p0, p1));
+        l1 = fadd2(l1, pk2(p2, p3));
+        sreg[i] = pack2<T>(p0, p1);      // 16-bit P pair i overwrites a slot already consumed (i <= 2i)
+        sreg[i + 1] = pack2<T>(p2, p3);
+      }
+      {
+        float a0, a1, a2, a3;
+        upk2(l0, a0, a1);
+        upk2(l1, a2, a3);
+        l += (a0 + a1) + (a2 + a3);
+      }
+      tmem_st32(tS + lane_sel, sreg);
+      tmem_st32(tS + lane_sel + 32, sreg + 32);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
