@@ -217,25 +217,22 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int n_half = 2 * n_it;
       bool ok = mbar_wait(bar_kv_full, 0, guard, kStBwdMma);
       // S^T / dP^T of half u (64 queries) into score buffer u & 1
+      constexpr uint32_t hi_k = desc_hi_sw128(1024);
+      const uint32_t k_lo = desc_lo_sw128(sK, 16), v_lo = desc_lo_sw128(sV, 16);
       auto issue_scores = [&](int u) -> bool {
         const int it = u >> 1, hf = u & 1, s = it % L::kStages;
         const uint32_t sQ = sRing + s * 2 * L::kTileBytes, sdO = sQ + L::kTileBytes;
+        const uint32_t q_lo = desc_lo_sw128(sQ + hf * 8192, 16), do_lo = desc_lo_sw128(sdO + hf * 8192, 16);
         if (hf == 0) {
           if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)(it / L::kStages) & 1u, guard, kStBwdMma)) return false;
           tc_fence_after();
         }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {  // S^T = K Q^T   (B = 64 query rows of the Q tile)
-          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tSt + hf * 64, smem_desc_sw128(sK + off, 16, 1024), smem_desc_sw128(sQ + off + hf * 8192, 16, 1024),
-                 idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)  // S^T = K Q^T   (B = 64 query rows of the Q tile)
+          mma_ss_lh(tSt + hf * 64, k_lo + kmajor_step(kk), q_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {  // dP^T = V dO^T
-          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tdPt + hf * 64, smem_desc_sw128(sV + off, 16, 1024), smem_desc_sw128(sdO + off + hf * 8192, 16, 1024),
-                 idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)  // dP^T = V dO^T
+          mma_ss_lh(tdPt + hf * 64, v_lo + kmajor_step(kk), do_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
         mma_commit(bar_s_full + 8 * hf);
         return true;
       };
@@ -243,6 +240,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int u = 0; u < n_half && ok; ++u) {
         const int it = u >> 1, hf = u & 1, s = it % L::kStages;
         const uint32_t sQ = sRing + s * 2 * L::kTileBytes, sdO = sQ + L::kTileBytes;
+        // MN-major B operands: the half's 64 query rows start 8 KB into each 64-channel block
+        const uint32_t qmn_lo = desc_lo_sw128(sQ + hf * 8192, kChunkBytes), domn_lo = desc_lo_sw128(sdO + hf * 8192, kChunkBytes);
         if (u + 1 < n_half) {
           ok = issue_scores(u + 1);  // tensor cores stay busy while half u is exponentiated
           if (!ok) break;
@@ -253,9 +252,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {  // dV += P^T dO ; dK += dS^T Q   (16 of the half's 64 queries per step)
           const uint32_t acol = hf * 64 + (kk / 2) * 32 + (kk % 2) * 8;
-          const uint32_t boff = (hf * 4 + kk) * 2048;
-          mma_ts(tdV, tSt + acol, smem_desc_sw128(sdO + boff, kChunkBytes, 1024), idesc_acc, (u > 0 || kk > 0));
-          mma_ts(tdK, tdPt + acol, smem_desc_sw128(sQ + boff, kChunkBytes, 1024), idesc_acc, (u > 0 || kk > 0));
+          mma_ts_lh(tdV, tSt + acol, domn_lo + kk * 128, hi_k, idesc_acc, (u > 0 || kk > 0));
+          mma_ts_lh(tdK, tdPt + acol, qmn_lo + kk * 128, hi_k, idesc_acc, (u > 0 || kk > 0));
         }
         if (hf == 1) mma_commit(bar_ring_empty + 8 * s);
       }
@@ -488,25 +486,22 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int n_half = 2 * n_it;
       bool ok = mbar_wait(bar_q_full, 0, guard, kStDqMma);
       // S / dP of half u (64 keys) into score buffer u & 1
+      constexpr uint32_t hi_k = desc_hi_sw128(1024);
+      const uint32_t q_lo = desc_lo_sw128(sQ, 16), do_lo = desc_lo_sw128(sdO, 16);
       auto issue_scores = [&](int u) -> bool {
         const int it = u >> 1, hf = u & 1, s = it % L::kStages;
         const uint32_t sK = sRing + s * 2 * L::kTileBytes, sV = sK + L::kTileBytes;
+        const uint32_t k_lo = desc_lo_sw128(sK + hf * 8192, 16), v_lo = desc_lo_sw128(sV + hf * 8192, 16);
         if (hf == 0) {
           if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)(it / L::kStages) & 1u, guard, kStDqMma)) return false;
           tc_fence_after();
         }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {  // S = Q K^T   (B = 64 key rows of the K tile)
-          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tS + hf * 64, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off + hf * 8192, 16, 1024),
-                 idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)  // S = Q K^T   (B = 64 key rows of the K tile)
+          mma_ss_lh(tS + hf * 64, q_lo + kmajor_step(kk), k_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {  // dP = dO V^T
-          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tdP + hf * 64, smem_desc_sw128(sdO + off, 16, 1024), smem_desc_sw128(sV + off + hf * 8192, 16, 1024),
-                 idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)  // dP = dO V^T
+          mma_ss_lh(tdP + hf * 64, do_lo + kmajor_step(kk), v_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
         mma_commit(bar_s_full + 8 * hf);
         return true;
       };
@@ -514,6 +509,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int u = 0; u < n_half && ok; ++u) {
         const int it = u >> 1, hf = u & 1, s = it % L::kStages;
         const uint32_t sK = sRing + s * 2 * L::kTileBytes;
+        const uint32_t kmn_lo = desc_lo_sw128(sK + hf * 8192, kChunkBytes);
         if (u + 1 < n_half) {
           ok = issue_scores(u + 1);
           if (!ok) break;
@@ -524,8 +520,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {  // dQ += dS K   (16 of the half's 64 keys per step)
           const uint32_t acol = hf * 64 + (kk / 2) * 32 + (kk % 2) * 8;
-          mma_ts(tdQ, tdP + acol, smem_desc_sw128(sK + (hf * 4 + kk) * 2048, kChunkBytes, 1024), idesc_acc,
-                 (u > 0 || kk > 0));
+          mma_ts_lh(tdQ, tdP + acol, kmn_lo + kk * 128, hi_k, idesc_acc, (u > 0 || kk > 0));
         }
         if (hf == 1) mma_commit(bar_ring_empty + 8 * s);
       }

@@ -181,20 +181,21 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
       constexpr uint32_t idesc_o = make_idesc<T>(kTile, D, false, true);
+      constexpr uint32_t hi_k = desc_hi_sw128(1024);  // both operand kinds: 8-row groups 1 KB apart
+      const uint32_t q_lo = desc_lo_sw128(sQ, 16);
       bool ok = mbar_wait(bar_q_full, 0, guard, kStMma);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % NSTAGE;
         const uint32_t ph = (uint32_t)(j / NSTAGE) & 1u;
+        const uint32_t k_lo = desc_lo_sw128(sK + s * L::kTileBytes, 16);
+        const uint32_t v_lo = desc_lo_sw128(sV + s * L::kTileBytes, kChunkBytes);  // MN-major: channel blocks 16 KB apart
         ok = mbar_wait(bar_k_full + 8 * s, ph, guard, kStMma);
         if (!ok) break;
         tc_fence_after();
         // S = Q K^T: both K-major; 16 channels (32 bytes) per instruction.
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          mma_ss(tS, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + s * L::kTileBytes + off, 16, 1024),
-                 idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss_lh(tS, q_lo + kmajor_step(kk), k_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0 ? 1u : 0u);
         mma_commit(bar_k_empty + 8 * s);
         mma_commit(bar_s_full);
         ok = mbar_wait(bar_p_full, (uint32_t)j & 1u, guard, kStMma);
@@ -202,13 +203,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         ok = mbar_wait(bar_v_full + 8 * s, ph, guard, kStMma);
         if (!ok) break;
         tc_fence_after();
-        // O += P V: P (128 x 128, 16-bit) from TMEM, 16 keys = 8 columns per instruction;
-        // V is MN-major: channel blocks 16 KB apart (LBO), 8-key groups 1 KB apart (SBO).
+        // O += P V: P (128 x 128, 16-bit) from TMEM, 16 keys = 8 columns and 2 KB of V per instruction.
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          mma_ts(tO, tS + kk * 8, smem_desc_sw128(sV + s * L::kTileBytes + kk * 2048, kChunkBytes, 1024), idesc_o,
-                 (j > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          mma_ts_lh(tO, tS + kk * 8, v_lo + kk * 128, hi_k, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         mma_commit(bar_v_empty + 8 * s);
       }
       if (ok) mma_commit(bar_o_full);
