@@ -272,25 +272,32 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     float* slot = rows_s + warp * 128;  // warp-private: [0,32) LSE, [64,96) delta of this warp's columns
     bool ok = true;
     const int n_half = 2 * n_it;
-    for (int u = 0; u < n_half; ++u) {
+    // -LSE and -delta of this lane's query column of half u; fetched one half ahead so the global
+    // load latency hides behind the exponentials of the current half.
+    auto fetch_rows = [&](int u, float& nl, float& nd) {
       const int it = u >> 1, hf = u & 1;
       const int h = hk * G + it / n_qt;
+      const int qrow = (qt_lo + it % n_qt) * kTile + hf * 64 + cw0 + lane;
+      nl = 0.f;
+      nd = 0.f;
+      if (qrow < g.Lq) {
+        const float lv = p.lse[b * p.lse_sb + h * p.lse_sh + qrow * p.lse_sl];
+        nl = (lv == -CUDART_INF_F) ? 0.f : -lv;
+        nd = -p.delta[((long long)b * g.H + h) * g.Lq + qrow];
+      }
+    };
+    float nl_next, nd_next;
+    fetch_rows(0, nl_next, nd_next);
+    for (int u = 0; u < n_half; ++u) {
+      const int it = u >> 1, hf = u & 1;
       const int qi = qt_lo + it % n_qt;
       const int qg0 = qi * kTile + g.q_off;
       const int cbase = hf * 64 + cw0;  // first of this warp's 32 query columns inside the tile
       __syncwarp();
-      {
-        const int qrow = qi * kTile + cbase + lane;
-        float lv = 0.f, dl = 0.f;
-        if (qrow < g.Lq) {
-          lv = p.lse[b * p.lse_sb + h * p.lse_sh + qrow * p.lse_sl];
-          if (lv == -CUDART_INF_F) lv = 0.f;
-          dl = p.delta[((long long)b * g.H + h) * g.Lq + qrow];
-        }
-        slot[lane] = -lv;  // negated: they enter the packed FMA / ADD as addends
-        slot[64 + lane] = -dl;
-      }
+      slot[lane] = nl_next;  // negated: they enter the packed FMA / ADD as addends
+      slot[64 + lane] = nd_next;
       __syncwarp();
+      if (u + 1 < n_half) fetch_rows(u + 1, nl_next, nd_next);
       ok = mbar_wait(bar_s_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStBwdCompute);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
@@ -378,12 +385,33 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ================================================================================ dQ
+// TMEM: two full-width score buffers S[2] (fp32, 128 columns each), dP (128, overlaid by the
+// 16-bit dS) and the dQ accumulator.  Every MMA runs at N = 128.  Tensor-core order per key tile u:
+//   dQ += dS(u) K(u)   (in two halves, each as soon as its 64 columns of dS are in TMEM)
+//   dP(u+1) = dO V(u+1)^T,   S(u+2) = Q K(u+2)^T
+// so the exponentials of tile u+1 overlap S(u+2) and the first half of the dQ GEMM.  K needs three
+// ring stages (S(u+2) is issued while K(u) is still read by the dQ GEMM), V two.
+template <int D>
+struct DqSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kKStages = 3, kVStages = 2;
+  static constexpr int kQ = 0;
+  static constexpr int kdO = kQ + kTileBytes;
+  static constexpr int kK = kdO + kTileBytes;
+  static constexpr int kV = kK + kKStages * kTileBytes;
+  static constexpr int kBars = kV + kVStages * kTileBytes;
+  static constexpr int kNumBars = 5 + 2 * kKStages + 2 * kVStages;
+  static constexpr int kMisc = kBars + 8 * kNumBars;
+  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
 template <typename T, int D, class M>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                  const __grid_constant__ CUtensorMap tmdQ, BwdTcParams p) {
-  using L = BwdSmem<D>;
+  using L = DqSmem<D>;
   constexpr int kChunks = D / 64;
   constexpr int kChunkBytes = kTile * 128;
   const Geo& g = p.g;
@@ -418,10 +446,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t sQ = base + L::kFixA, sdO = base + L::kFixB, sRing = base + L::kRing;
+  const uint32_t sQ = base + L::kQ, sdO = base + L::kdO, sKr = base + L::kK, sVr = base + L::kV;
   const uint32_t bars = base + L::kBars;
-  const uint32_t bar_q_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_p_full = bars + 32;
-  const uint32_t bar_ring_full = bars + 48, bar_ring_empty = bar_ring_full + 8 * L::kStages;
+  const uint32_t bar_q_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_p_full = bars + 24;  // p_full[2]
+  const uint32_t bar_k_full = bars + 40, bar_k_empty = bar_k_full + 8 * L::kKStages;
+  const uint32_t bar_v_full = bar_k_empty + 8 * L::kKStages, bar_v_empty = bar_v_full + 8 * L::kVStages;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
   const Guard guard{p.status, abort_flag};
@@ -430,13 +459,16 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     *abort_flag = 0;
     mbar_init(bar_q_full, 1);
     mbar_init(bar_acc_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_p_full + 8 * i, kBwdComputeThreads / 32);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_p_full, kBwdComputeThreads / 32);
+    mbar_init(bar_p_full + 8, kBwdComputeThreads / 32);
+    for (int s = 0; s < L::kKStages; ++s) {
+      mbar_init(bar_k_full + 8 * s, 1);
+      mbar_init(bar_k_empty + 8 * s, 1);
     }
-    for (int s = 0; s < L::kStages; ++s) {
-      mbar_init(bar_ring_full + 8 * s, 1);
-      mbar_init(bar_ring_empty + 8 * s, 1);
+    for (int s = 0; s < L::kVStages; ++s) {
+      mbar_init(bar_v_full + 8 * s, 1);
+      mbar_init(bar_v_empty + 8 * s, 1);
     }
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -449,9 +481,10 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
+  const uint32_t tS = tmem, tdP = tmem + 256, tdQ = tmem + 384;  // S buffer i at tS + 128 i
 
   if (warp == 8) {
+    // --------------------------------------------------------------------- TMA producer
     if (lane == 0) {
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
@@ -462,17 +495,18 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       bool ok = true;
       for (int it = 0; it < n_it; ++it) {
-        const int s = it % L::kStages;
-        const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
+        const int ks = it % L::kKStages, vs = it % L::kVStages;
         const int krow = (kt_lo + it) * kTile;
-        ok = mbar_wait(bar_ring_empty + 8 * s, ph ^ 1u, guard, kStDqProducer);
+        ok = mbar_wait(bar_k_empty + 8 * ks, ((uint32_t)(it / L::kKStages) & 1u) ^ 1u, guard, kStDqProducer);
         if (!ok) break;
-        mbar_arrive_expect_tx(bar_ring_full + 8 * s, 2 * L::kTileBytes);
-        const uint32_t dst = sRing + s * 2 * L::kTileBytes;
-        for (int c = 0; c < kChunks; ++c) {
-          tma_load_4d(dst + c * kChunkBytes, &tmK, bar_ring_full + 8 * s, c * 64, krow, hk, b);
-          tma_load_4d(dst + L::kTileBytes + c * kChunkBytes, &tmV, bar_ring_full + 8 * s, c * 64, krow, hk, b);
-        }
+        mbar_arrive_expect_tx(bar_k_full + 8 * ks, L::kTileBytes);
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_4d(sKr + ks * L::kTileBytes + c * kChunkBytes, &tmK, bar_k_full + 8 * ks, c * 64, krow, hk, b);
+        ok = mbar_wait(bar_v_empty + 8 * vs, ((uint32_t)(it / L::kVStages) & 1u) ^ 1u, guard, kStDqProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_v_full + 8 * vs, L::kTileBytes);
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_4d(sVr + vs * L::kTileBytes + c * kChunkBytes, &tmV, bar_v_full + 8 * vs, c * 64, krow, hk, b);
       }
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
@@ -480,57 +514,65 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 9) {
+    // ----------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc<T>(kTile, 64, false, false);
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
       constexpr uint32_t idesc_acc = make_idesc<T>(kTile, D, false, true);
-      const int n_half = 2 * n_it;
-      bool ok = mbar_wait(bar_q_full, 0, guard, kStDqMma);
-      // S / dP of half u (64 keys) into score buffer u & 1
       constexpr uint32_t hi_k = desc_hi_sw128(1024);
       const uint32_t q_lo = desc_lo_sw128(sQ, 16), do_lo = desc_lo_sw128(sdO, 16);
-      auto issue_scores = [&](int u) -> bool {
-        const int it = u >> 1, hf = u & 1, s = it % L::kStages;
-        const uint32_t sK = sRing + s * 2 * L::kTileBytes, sV = sK + L::kTileBytes;
-        const uint32_t k_lo = desc_lo_sw128(sK + hf * 8192, 16), v_lo = desc_lo_sw128(sV + hf * 8192, 16);
-        if (hf == 0) {
-          if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)(it / L::kStages) & 1u, guard, kStDqMma)) return false;
-          tc_fence_after();
-        }
+      bool ok = mbar_wait(bar_q_full, 0, guard, kStDqMma);
+      auto issue_s = [&](int it) -> bool {  // S(it) = Q K(it)^T into score buffer it & 1
+        const int ks = it % L::kKStages;
+        if (!mbar_wait(bar_k_full + 8 * ks, (uint32_t)(it / L::kKStages) & 1u, guard, kStDqMma)) return false;
+        tc_fence_after();
+        const uint32_t k_lo = desc_lo_sw128(sKr + ks * L::kTileBytes, 16);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)  // S = Q K^T   (B = 64 key rows of the K tile)
-          mma_ss_lh(tS + hf * 64, q_lo + kmajor_step(kk), k_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)  // dP = dO V^T
-          mma_ss_lh(tdP + hf * 64, do_lo + kmajor_step(kk), v_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
-        mma_commit(bar_s_full + 8 * hf);
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss_lh(tS + (it & 1) * 128, q_lo + kmajor_step(kk), k_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
         return true;
       };
-      if (ok) ok = issue_scores(0);
-      for (int u = 0; u < n_half && ok; ++u) {
-        const int it = u >> 1, hf = u & 1, s = it % L::kStages;
-        const uint32_t sK = sRing + s * 2 * L::kTileBytes;
-        const uint32_t kmn_lo = desc_lo_sw128(sK + hf * 8192, kChunkBytes);
-        if (u + 1 < n_half) {
-          ok = issue_scores(u + 1);
-          if (!ok) break;
-        }
-        ok = mbar_wait(bar_p_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStDqMma);
-        if (!ok) break;
+      auto issue_dp = [&](int it) -> bool {  // dP(it) = dO V(it)^T; then both scores of tile `it` are complete
+        const int vs = it % L::kVStages;
+        if (!mbar_wait(bar_v_full + 8 * vs, (uint32_t)(it / L::kVStages) & 1u, guard, kStDqMma)) return false;
         tc_fence_after();
+        const uint32_t v_lo = desc_lo_sw128(sVr + vs * L::kTileBytes, 16);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {  // dQ += dS K   (16 of the half's 64 keys per step)
-          const uint32_t acol = hf * 64 + (kk / 2) * 32 + (kk % 2) * 8;
-          mma_ts_lh(tdQ, tdP + acol, kmn_lo + kk * 128, hi_k, idesc_acc, (u > 0 || kk > 0));
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss_lh(tdP, do_lo + kmajor_step(kk), v_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
+        mma_commit(bar_v_empty + 8 * vs);
+        mma_commit(bar_s_full);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      if (ok) ok = issue_dp(0);
+      if (ok && n_it > 1) ok = issue_s(1);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int ks = it % L::kKStages;
+        const uint32_t kmn_lo = desc_lo_sw128(sKr + ks * L::kTileBytes, kChunkBytes);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {  // dQ += dS K, 64 keys at a time as their dS lands in TMEM
+          ok = mbar_wait(bar_p_full + 8 * hf, (uint32_t)it & 1u, guard, kStDqMma);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int kk = hf * 4 + j;
+            const uint32_t acol = hf * 64 + (j / 2) * 32 + (j % 2) * 8;
+            mma_ts_lh(tdQ, tdP + acol, kmn_lo + kk * 128, hi_k, idesc_acc, (it > 0 || kk > 0));
+          }
         }
-        if (hf == 1) mma_commit(bar_ring_empty + 8 * s);
+        if (!ok) break;
+        mma_commit(bar_k_empty + 8 * ks);
+        if (it + 1 < n_it) ok = issue_dp(it + 1);
+        if (ok && it + 2 < n_it) ok = issue_s(it + 2);
       }
       if (ok) mma_commit(bar_acc_full);
     }
   } else {
+    // ------------------------------------------------------------------- compute warps
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;  // query row inside the tile
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const int cw0 = wg * 32;
     const int qg = qg0 + r;
     const bool row_ok = qg < n && qb + r < g.Lq;
     const float c = g.scale * kLog2e;
@@ -541,56 +583,58 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       delta = p.delta[((long long)b * g.H + h) * g.Lq + qb + r];
     }
     if (!row_ok) lse = CUDART_INF_F;  // padded query rows: 2^(x - inf) = 0, so they contribute nothing and stay finite
+    const uint64_t c2 = pk2(c, c), nl2 = pk2(-lse, -lse), nd2 = pk2(-delta, -delta);
     bool ok = true;
-    const int n_half = 2 * n_it;
-    for (int u = 0; u < n_half; ++u) {
-      const int it = u >> 1, hf = u & 1;
+    for (int it = 0; it < n_it; ++it) {
       const int kt = kt_lo + it;
       const int kg0 = kt * kTile + g.k_off;
-      const int cbase = hf * 64 + cw0;  // first of this warp's 32 key columns inside the tile
-      ok = mbar_wait(bar_s_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStDqCompute);
+      ok = mbar_wait(bar_s_full, (uint32_t)it & 1u, guard, kStDqCompute);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
                         kt * kTile + kTile <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * kTile);
-      uint32_t sreg[32], dpreg[32], dsreg[16];
-      tmem_ld32(tS + lane_sel + cbase, sreg);
-      tmem_ld32(tdP + lane_sel + cbase, dpreg);
-      tmem_wait_ld();
-      const uint64_t c2 = pk2(c, c), nl2 = pk2(-lse, -lse), nd2 = pk2(-delta, -delta);
-      auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
-        constexpr bool kMasked = decltype(masked_tag)::value;
+      const uint32_t tSb = tS + (it & 1) * 128;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {  // packed fp32 pairs; lse = +inf on padded rows gives p = 0
-          float p0, p1, d0, d1;
-          upk2(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nl2), p0, p1);
-          p0 = ex2(p0);
-          p1 = ex2(p1);
-          if (kMasked) {
-            const int col = cbase + 2 * i;
-            p0 = (col < klim && M::mask(qg, kg0 + col, n, g.margs)) ? p0 : 0.f;
-            p1 = (col + 1 < klim && M::mask(qg, kg0 + col + 1, n, g.margs)) ? p1 : 0.f;
+      for (int hf = 0; hf < 2; ++hf) {
+        const int cbase = hf * 64 + wg * 32;  // this warp's 32 key columns of the half
+        uint32_t sreg[32], dpreg[32], dsreg[16];
+        tmem_ld32(tSb + lane_sel + cbase, sreg);
+        tmem_ld32(tdP + lane_sel + cbase, dpreg);
+        tmem_wait_ld();
+        auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
+          constexpr bool kMasked = decltype(masked_tag)::value;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {  // packed fp32 pairs; lse = +inf on padded rows gives p = 0
+            float p0, p1, d0, d1;
+            upk2(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nl2), p0, p1);
+            p0 = ex2(p0);
+            p1 = ex2(p1);
+            if (kMasked) {
+              const int col = cbase + 2 * i;
+              p0 = (col < klim && M::mask(qg, kg0 + col, n, g.margs)) ? p0 : 0.f;
+              p1 = (col + 1 < klim && M::mask(qg, kg0 + col + 1, n, g.margs)) ? p1 : 0.f;
+            }
+            upk2(fmul2(pk2(p0, p1), fadd2(pk2u(dpreg[2 * i], dpreg[2 * i + 1]), nd2)), d0, d1);
+            dsreg[i] = pack2<T>(d0, d1);
           }
-          upk2(fmul2(pk2(p0, p1), fadd2(pk2u(dpreg[2 * i], dpreg[2 * i + 1]), nd2)), d0, d1);
-          dsreg[i] = pack2<T>(d0, d1);
-        }
-      };
-      if (full) body(std::false_type{});
-      else body(std::true_type{});
-      tmem_st16(tdP + lane_sel + cbase, dsreg);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full + 8 * hf);  // one arrival per compute warp
+        };
+        if (full) body(std::false_type{});
+        else body(std::true_type{});
+        tmem_st16(tdP + lane_sel + cbase, dsreg);  // 16-bit dS over the dP columns this warp just consumed
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p_full + 8 * hf);  // one arrival per compute warp
+      }
     }
 
     // ---- epilogue: dQ * sm_scale; warps 0-3 take channels [0, D/2), warps 4-7 the rest
     if (ok) ok = mbar_wait(bar_acc_full, 0, guard, kStDqEpilogue);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
-    uint8_t* stage = gen_base + L::kRing;
+    uint8_t* stage = gen_base + L::kK;
 #pragma unroll
     for (int qq = 0; qq < D / 64; ++qq) {
       const int q4 = wg * (D / 64) + qq;
@@ -604,7 +648,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     fence_proxy_async_smem();
     named_bar_sync(1, kBwdComputeThreads);
     if (threadIdx.x == 0) {
-      for (int cc = 0; cc < kChunks; ++cc) tma_store_4d(&tmdQ, sRing + cc * kChunkBytes, cc * 64, qb, h, b);
+      for (int cc = 0; cc < kChunks; ++cc) tma_store_4d(&tmdQ, sKr + cc * kChunkBytes, cc * 64, qb, h, b);
       tma_store_commit();
       tma_store_wait_all();
     }
@@ -621,13 +665,15 @@ int launch_bwd_one(const CUtensorMap* maps, const BwdTcParams& p, cudaStream_t s
   auto kdkdv = bwd_dkdv_tc_kernel<T, D, M>;
   auto kdq = bwd_dq_tc_kernel<T, D, M>;
   constexpr int smem = BwdSmem<D>::kDynamic;
+  constexpr int smem_dq = DqSmem<D>::kDynamic;
+  static_assert(smem_dq <= 232448 && smem <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
     cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq);
     if (e != cudaSuccess) return (int)e;
     configured_dev = dev;
   }
@@ -641,7 +687,7 @@ int launch_bwd_one(const CUtensorMap* maps, const BwdTcParams& p, cudaStream_t s
   }
   if (p.which & 2) {
     dim3 gq((g.Lq + kTile - 1) / kTile, g.H, g.B);
-    kdq<<<gq, kBwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+    kdq<<<gq, kBwdThreads, smem_dq, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   }
   return (int)cudaGetLastError();
 }
