@@ -1,0 +1,63 @@
+"""Sequence-sharded attention on 2 GPUs (NCCL halo exchange + the CUDA kernels with global offsets).
+Skipped on a single-GPU box; the partition logic itself is covered on CPU ranks in test_dist_cpu.py."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import ROOT, ensure_built
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, mask_name, mask_args, L, dtype_name):
+    for p in (os.path.join(ROOT, "chill-attention_b200"), ROOT, os.path.join(ROOT, "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import chill_attention as ca
+        from chill_attention import _cabi
+        from chill_attention import dist as cdist
+        from helpers import G_RTOL, O_ATOL
+        from oracle import attention_oracle as orc
+
+        dtype = getattr(torch, dtype_name)
+        mask = getattr(ca, mask_name)(*mask_args)
+        g = torch.Generator().manual_seed(11)
+        B, H, Hkv, D = 1, 4, 2, 128
+        q, do = (torch.randn(B, H, L, D, generator=g).to(dtype) for _ in range(2))
+        k, v = (torch.randn(B, Hkv, L, D, generator=g).to(dtype) for _ in range(2))
+        Ls = L // world
+        sl = slice(rank * Ls, (rank + 1) * Ls)
+        ql, kl, vl = (t[:, :, sl].cuda().requires_grad_(True) for t in (q, k, v))
+        o = cdist.sequence_sharded_attention(ql, kl, vl, mask, L)
+        o.backward(do[:, :, sl].cuda())
+        torch.cuda.synchronize()
+        assert _cabi.load_library().chill_read_device_status() == 0
+        pos = torch.arange(L)
+        md = orc.builtin_mask_dense(mask.name, mask.constargs, pos, pos)
+        o_ref, _ = orc.attention_forward(md, q.double(), k.double(), v.double())
+        grads = orc.attention_backward(md, q.double(), k.double(), v.double(), do.double())
+        assert (o.detach().cpu().double() - o_ref[:, :, sl]).abs().max() <= O_ATOL[dtype]
+        for mine, ref in zip((ql.grad, kl.grad, vl.grad), grads):
+            ref = ref[:, :, sl]
+            rel = ((mine.cpu().double() - ref).norm() / ref.norm()).item()
+            assert rel <= 1.5 * G_RTOL[dtype], rel  # halo rows are rounded once more when two partial sums are added
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mask", [("SlidingWindowChillMask", (300, 0)), ("SlidingWindowChillMask", (200, 70)),
+                                  ("ChunkwiseChillMask", (128, 2))], ids=str)
+def test_sequence_sharded_on_two_gpus(mask):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ensure_built()
+    port = 29600 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, mask[0], mask[1], 2048, "bfloat16"), nprocs=2, join=True)
