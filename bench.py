@@ -51,6 +51,10 @@ import torch  # noqa: E402
 METRIC = "effective TFLOP/s (unmasked FLOPs) fwd & fwd+bwd, % of B200 dense BF16 peak"
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
+# dram__bytes_read.sum + dram__bytes_write.sum per (batch, head) unit from the ncu capture summarised in
+# profiles/c2s_causal_bf16_kernels_ncu.md (causal bf16 L=4096 D=128, 32 units per launch); traffic grows in
+# proportion to the units a launch processes, so a full launch = per-unit figure x B x H.
+NCU_DRAM_BYTES_PER_UNIT = {("c2", "fwd"): 117.4e6 / 32, ("c2", "dkdv"): 177.8e6 / 32, ("c2", "dq"): 158.1e6 / 32}
 
 WORKLOADS = {
     # name: (mask class, mask args, dtype, B, H, L, D)
@@ -296,7 +300,9 @@ def run_ours(args):
                         "pct_of_nominal_peak": round(100 * value / world / NOMINAL_BF16_TFLOPS, 2)},
             "kernel_ms": {kn: round(per_kernel[kn], 4) for kn in kernels},
             "roofline": {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 2), "peak": peak,
-                         "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
+                         "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
+                         "traffic": (round(NCU_DRAM_BYTES_PER_UNIT[(args.workload.rstrip("s"), dom)] * B * H)
+                                     if (args.workload.rstrip("s"), dom) in NCU_DRAM_BYTES_PER_UNIT else None),
                          "peak_source": f"{peak_src} cuBLAS bf16 burst (sustained {peak_sustained})",
                          "flops_per_launch": kflops[dom] * B * H * D * pairs},
             "gpu_launches": 4 * args.steps,
