@@ -394,19 +394,81 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_triton_reference(args):
+    """Extra arm (not the driver's reference arm): the reference's own Triton kernels on this GPU,
+    through its public API, if an unmodified copy of its package sits in baseline/_ref (git-ignored;
+    its pip install produces an empty package because of `py-modules` in its pyproject.toml)."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    if not os.path.isdir(os.path.join(ref_dir, "chill_attention")) or not torch.cuda.is_available():
+        print(json.dumps({"impl": "triton", "unavailable": "baseline/_ref/chill_attention or CUDA device not present"}))
+        return
+    sys.path.insert(0, ref_dir)
+    import chill_attention as ref  # the reference, not this repository's package
+
+    assert os.path.realpath(ref.__file__).startswith(os.path.realpath(ref_dir)), ref.__file__
+    mname, margs, dt, B, H, L, D = WORKLOADS[args.workload]
+    dtype = getattr(torch, dt)
+    mask = getattr(ref, mname)(*margs)
+    pos = torch.arange(L, dtype=torch.int64)
+    pairs = {"FullChillMask": L * L, "CausalChillMask": L * (L + 1) // 2}.get(mname)
+    if pairs is None:
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("own_mask", os.path.join(ROOT, "chill-attention_b200", "chill_attention", "mask.py"))
+        own = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(own)
+        pairs = unmasked_pairs(getattr(own, mname)(*margs), L)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(20)
+    q, k, v, do = (torch.randn(B, H, L, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    out = {}
+    for autotune in ((False, True) if args.triton_autotune else (False,)):
+        def fwd():
+            with torch.no_grad():
+                return ref.chill_attention(q, k, v, mask=mask, autotune=autotune)
+
+        def fwd_bwd():
+            q.grad = k.grad = v.grad = None
+            ref.chill_attention(q, k, v, mask=mask, autotune=autotune).backward(do)
+
+        res = {}
+        for name, fn, flops in (("fwd", fwd, 4.0), ("fwd_bwd", fwd_bwd, 14.0)):
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            res[name] = {"ms": round(ms, 4), "tflops": round(flops * B * H * D * pairs / (ms * 1e-3) / 1e12, 2)}
+        out["autotune" if autotune else "default_tables"] = res
+    print(json.dumps({"impl": "triton", "metric": METRIC, "unit": "TFLOP/s", "config": {"workload": describe(args.workload)},
+                      "results": out, "note": "reference Triton kernels (triton %s) through chill_attention(), outputs allocated "
+                      "and zero-filled by the reference inside the timed region" % __import__("triton").__version__}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference", "triton"))
+    ap.add_argument("--triton-autotune", action="store_true", help="--impl triton: also time autotune=True")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work per baseline sample")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.impl == "triton":
+        run_triton_reference(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
