@@ -60,13 +60,14 @@ def build_library(out_path=None, custom_header=None, custom_functor=None, verbos
     """Compile and link the library; returns its path.  Skips work when sources are unchanged."""
     out_path = out_path or os.path.join(LIB_DIR, "libchill_b200.so")
     os.makedirs(os.path.dirname(out_path), exist_ok=True)
-    defines, functors = [], list(BUILTIN_FUNCTORS)
-    extra = ()
+    # CHILL_B200_NVCC_FLAGS: extra compiler flags, e.g. "-DCHILL_FWD_POLY_NUM=1 -DCHILL_FWD_POLY_DEN=4"
+    defines, functors = os.environ.get("CHILL_B200_NVCC_FLAGS", "").split(), list(BUILTIN_FUNCTORS)
+    extra = tuple(defines)
     if custom_header is not None:
         custom_header = os.path.abspath(custom_header)
         with open(custom_header, "rb") as f:
-            extra = (custom_functor, hashlib.sha256(f.read()).hexdigest())
-        defines = [f'-DCHILL_CUSTOM_MASK_HEADER="{custom_header}"', f"-DCHILL_CUSTOM_MASK={custom_functor}"]
+            extra = extra + (custom_functor, hashlib.sha256(f.read()).hexdigest())
+        defines = defines + [f'-DCHILL_CUSTOM_MASK_HEADER="{custom_header}"', f"-DCHILL_CUSTOM_MASK={custom_functor}"]
         functors.append(custom_functor)
     digest = _sources_digest(extra)
     stamp = out_path + ".stamp"

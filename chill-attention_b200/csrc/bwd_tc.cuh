@@ -318,12 +318,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const float4 nl4 = reinterpret_cast<const float4*>(slot)[j];
           const float4 nd4 = reinterpret_cast<const float4*>(slot + 64)[j];
           float p0, p1, p2, p3, d0, d1, d2, d3;
-          upk2(ffma2(pk2u(sreg[4 * j], sreg[4 * j + 1]), c2, pk2(nl4.x, nl4.y)), p0, p1);
-          upk2(ffma2(pk2u(sreg[4 * j + 2], sreg[4 * j + 3]), c2, pk2(nl4.z, nl4.w)), p2, p3);
-          p0 = ex2(p0);
-          p1 = ex2(p1);
-          p2 = ex2(p2);
-          p3 = ex2(p3);
+          upk2(ex2_pair(ffma2(pk2u(sreg[4 * j], sreg[4 * j + 1]), c2, pk2(nl4.x, nl4.y)),
+                        ((2 * j) % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM), p0, p1);
+          upk2(ex2_pair(ffma2(pk2u(sreg[4 * j + 2], sreg[4 * j + 3]), c2, pk2(nl4.z, nl4.w)),
+                        ((2 * j + 1) % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM), p2, p3);
           if (kMasked) {
             const int cq = cbase + 4 * j;
             p0 = (key_ok && cq < qlim && M::mask(qg0 + cq, kg, n, g.margs)) ? p0 : 0.f;
@@ -608,9 +606,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 16; ++i) {  // packed fp32 pairs; lse = +inf on padded rows gives p = 0
             float p0, p1, d0, d1;
-            upk2(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nl2), p0, p1);
-            p0 = ex2(p0);
-            p1 = ex2(p1);
+            upk2(ex2_pair(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nl2), (i % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM),
+                 p0, p1);
             if (kMasked) {
               const int col = cbase + 2 * i;
               p0 = (col < klim && M::mask(qg, kg0 + col, n, g.margs)) ? p0 : 0.f;

@@ -281,15 +281,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       uint64_t l0 = 0ull, l1 = 0ull;  // two packed partial row sums (+0.0f, +0.0f)
 #pragma unroll
       for (int i = 0; i < kTile / 2; i += 2) {
+        // two pairs per step; a fixed share of the pairs takes the polynomial 2^x (FMA pipe), the rest MUFU
+        const uint64_t e0 = ex2_pair(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nm2),
+                                     (i % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
+        const uint64_t e1 = ex2_pair(ffma2(pk2u(sreg[2 * i + 2], sreg[2 * i + 3]), c2, nm2),
+                                     ((i + 1) % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
+        l0 = fadd2(l0, e0);
+        l1 = fadd2(l1, e1);
         float p0, p1, p2, p3;
-        upk2(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nm2), p0, p1);
-        upk2(ffma2(pk2u(sreg[2 * i + 2], sreg[2 * i + 3]), c2, nm2), p2, p3);
-        p0 = ex2(p0);
-        p1 = ex2(p1);
-        p2 = ex2(p2);
-        p3 = ex2(p3);
-        l0 = fadd2(l0, pk2(p0, p1));
-        l1 = fadd2(l1, pk2(p2, p3));
+        upk2(e0, p0, p1);
+        upk2(e1, p2, p3);
         sreg[i] = pack2<T>(p0, p1);      // 16-bit P pair i overwrites a slot already consumed (i <= 2i)
         sreg[i + 1] = pack2<T>(p2, p3);
       }

@@ -311,6 +311,58 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
+
+// 2^x for a packed pair on the FMA pipe instead of the MUFU unit (which delivers only 16 ex2 per
+// clock per SM and is the co-bottleneck of attention next to the tensor cores).  Cody-Waite split
+// x = n + f with n = round(x) via the 1.5 * 2^23 trick, f in [-0.5, 0.5]; 2^f by a degree-3
+// minimax polynomial (max relative error 7.5e-5, below fp16/bf16 resolution of the P operand it
+// feeds); the exponent is patched in with one integer multiply-add per element.  x is clamped to
+// [-126, ...) so that -inf (masked) and very negative arguments give ~0 instead of garbage.
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
+  float x0, x1;
+  upk2(x2, x0, x1);
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  x2 = pk2(x0, x1);
+  const uint64_t magic = pk2(12582912.f, 12582912.f), nmagic = pk2(-12582912.f, -12582912.f);
+  const uint64_t r2 = fadd2(x2, magic);                                  // low mantissa bits = n
+  const uint64_t f2 = ffma2(fadd2(r2, nmagic), pk2(-1.f, -1.f), x2);     // f = x - n
+  uint64_t p2 = pk2(0.0551716648f, 0.0551716648f);
+  p2 = ffma2(p2, f2, pk2(0.2426111251f, 0.2426111251f));
+  p2 = ffma2(p2, f2, pk2(0.6932609677f, 0.6932609677f));
+  p2 = ffma2(p2, f2, pk2(0.9999280572f, 0.9999280572f));
+  uint32_t pl, ph, rl, rh;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(pl), "=r"(ph) : "l"(p2));
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(rl), "=r"(rh) : "l"(r2));
+  pl += rl << 23;  // (bits(1.5 * 2^23 + n) << 23) == n << 23 in 32 bits
+  ph += rh << 23;
+  return pk2u(pl, ph);
+}
+
+// Share of the exponentials moved from MUFU to the polynomial: pairs with (index % DEN) < NUM.
+// Default 0: measured on B200 (causal and full masks, L = 4096, D = 128) every non-zero share made the
+// forward slower (0.60 ms at 0 %, 0.62 at 25 %, 0.65 at 50 %, 0.67 at 75 %) and the backward no faster:
+// the kernels are bound by the dependency chain between MMA and softmax phases, not by MUFU throughput.
+// The path is kept (and covered by the parity tests when enabled) for shapes where that changes.
+#ifndef CHILL_FWD_POLY_NUM
+#define CHILL_FWD_POLY_NUM 0
+#endif
+#ifndef CHILL_FWD_POLY_DEN
+#define CHILL_FWD_POLY_DEN 2
+#endif
+#ifndef CHILL_BWD_POLY_NUM
+#define CHILL_BWD_POLY_NUM 0
+#endif
+#ifndef CHILL_BWD_POLY_DEN
+#define CHILL_BWD_POLY_DEN 2
+#endif
+__device__ __forceinline__ uint64_t ex2_pair(uint64_t x2, bool poly) {
+  if (poly) return ex2_poly2(x2);
+  float a, b;
+  upk2(x2, a, b);
+  return pk2(ex2(a), ex2(b));
+}
+
 // Register re-allocation between warpgroups (all four warps of a warpgroup execute it).
 template <int N>
 __device__ __forceinline__ void reg_alloc() {
