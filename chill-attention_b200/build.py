@@ -91,6 +91,7 @@ def build_library(out_path=None, custom_header=None, custom_functor=None, verbos
     _run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out_path] + objs)
     with open(stamp, "w") as f:
         f.write(digest)
+    shutil.rmtree(obj_dir, ignore_errors=True)  # objects are not needed once linked
     return out_path
 
 
