@@ -1,0 +1,88 @@
+"""Forward + backward for callers whose tensors live in HOST memory.
+
+``attention_fwd_bwd_host`` streams the batch through the GPU in chunks on three CUDA streams
+(host->device copies, kernels, device->host copies) with double-buffered device staging, so the
+PCIe transfers in both directions overlap each other and the kernels.  It drives the C ABI
+directly (forward, delta, dK/dV, dQ), no autograd graph.  Host tensors should be pinned
+(``tensor.pin_memory()``); pageable memory works but serialises the copies.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+from .chill import _resolve_functor
+from .mask import ChillMask
+
+
+def attention_fwd_bwd_host(q, k, v, do, mask: ChillMask, sm_scale=None, out=None, chunk_batches: int = 1,
+                           device=None):
+    """q, do: [B, H, L, D]; k, v: [B, H_kv, L, D] on the host.  Returns host tensors (o, dq, dk, dv)
+    (pinned; pass ``out=(o, dq, dk, dv)`` to reuse buffers).  Synchronises before returning."""
+    device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+    B, H, L, D = q.shape
+    Hkv = k.shape[1]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    lib, functor = _resolve_functor(mask)
+    if out is None:
+        out = tuple(torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, q, k, v))
+    o_h, dq_h, dk_h, dv_h = out
+    cb = max(1, min(chunk_batches, B))
+    with torch.cuda.device(device):
+        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        start = torch.cuda.Event()
+        start.record()  # everything below is ordered after work already queued on the caller's stream
+        for s in (s_in, s_cmp, s_out):
+            s.wait_event(start)
+
+        def dev(shape, dtype):
+            return torch.empty(shape, dtype=dtype, device=device)
+
+        slots = []
+        for _ in range(2):
+            slots.append({
+                "in": [dev((cb, H, L, D), q.dtype), dev((cb, Hkv, L, D), q.dtype), dev((cb, Hkv, L, D), q.dtype),
+                       dev((cb, H, L, D), q.dtype)],
+                "out": [dev((cb, H, L, D), q.dtype), dev((cb, H, L, D), q.dtype), dev((cb, Hkv, L, D), q.dtype),
+                        dev((cb, Hkv, L, D), q.dtype)],
+                "lse": dev((cb, H, L), torch.float32), "delta": dev((cb, H, L), torch.float32),
+                "in_free": None, "out_free": None,
+            })
+        for i, b0 in enumerate(range(0, B, cb)):
+            b1 = min(B, b0 + cb)
+            n = b1 - b0
+            sl = slots[i % 2]
+            qd, kd, vd, dod = (t[:n] for t in sl["in"])
+            od, dqd, dkd, dvd = (t[:n] for t in sl["out"])
+            with torch.cuda.stream(s_in):
+                if sl["in_free"] is not None:
+                    s_in.wait_event(sl["in_free"])
+                for dst, src in zip((qd, kd, vd, dod), (q, k, v, do)):
+                    dst.copy_(src[b0:b1], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in)
+                if sl["out_free"] is not None:
+                    s_cmp.wait_event(sl["out_free"])
+                shape = _cabi.make_shape(qd, kd, functor, mask.constargs, None, sm_scale)
+                _cabi.forward(lib, qd, kd, vd, od, sl["lse"][:n], shape)
+                _cabi.backward(lib, qd, kd, vd, od, dod, sl["lse"][:n], sl["delta"][:n], dqd, dkd, dvd, shape)
+                ev_cmp = torch.cuda.Event()
+                ev_cmp.record(s_cmp)
+                sl["in_free"] = ev_cmp
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp)
+                for dst, src in zip((o_h, dq_h, dk_h, dv_h), (od, dqd, dkd, dvd)):
+                    dst[b0:b1].copy_(src, non_blocking=True)
+                ev_out = torch.cuda.Event()
+                ev_out.record(s_out)
+                sl["out_free"] = ev_out
+        cur = torch.cuda.current_stream()
+        for s in (s_in, s_cmp, s_out):
+            ev = torch.cuda.Event()
+            ev.record(s)
+            cur.wait_event(ev)
+        cur.synchronize()
+    return o_h, dq_h, dk_h, dv_h

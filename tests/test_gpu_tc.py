@@ -157,3 +157,18 @@ def test_torch_compile_traces_the_op():
     torch.library.opcheck(torch.ops.chill_attention.forwardCausalChillMask.default,
                           (qd.detach(), kd.detach(), vd.detach(), None, [], 0.125, True, False, "ieee", False),
                           test_utils=("test_schema", "test_faketensor"))
+
+
+def test_host_buffer_pipeline_matches_device_path():
+    import chill_attention as ca
+    from chill_attention.host import attention_fwd_bwd_host
+
+    mask = ca.CausalChillMask()
+    q, k, v, do = make_inputs(5, 4, 2, 384, 128, torch.bfloat16)
+    o, lse, grads = run(mask, q, k, v, do)
+    host = [t.pin_memory() for t in (q, k, v, do)]
+    for chunk in (1, 2, 8):
+        oh, dqh, dkh, dvh = attention_fwd_bwd_host(*host, mask, chunk_batches=chunk)
+        assert torch.equal(oh, o.detach().cpu())
+        for a, b in zip((dqh, dkh, dvh), grads):
+            assert torch.equal(a, b.cpu())
