@@ -19,7 +19,7 @@ def attention_fwd_bwd_host(q, k, v, do, mask: ChillMask, sm_scale=None, out=None
                            device=None):
     """q, do: [B, H, L, D]; k, v: [B, H_kv, L, D] on the host.  Returns host tensors (o, dq, dk, dv)
     (pinned; pass ``out=(o, dq, dk, dv)`` to reuse buffers).  Synchronises before returning."""
-    device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+    device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     B, H, L, D = q.shape
     Hkv = k.shape[1]
     if sm_scale is None:

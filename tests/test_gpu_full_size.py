@@ -75,8 +75,9 @@ def test_sampled_rows_and_identities(name):
             dq_ref, _, _ = orc.attention_backward(md, qs, ks, vs, dos, None, None, torch.float64, torch.tensor([r]), kp, L)
             assert (o[bi, hi, r].cpu().double() - o_ref[0, 0, 0]).abs().max() <= O_ATOL[dtype], (name, r)
             assert abs(lse[bi, hi, r].item() - lse_ref[0, 0, 0].item()) <= 1e-3 * max(1.0, abs(lse_ref[0, 0, 0].item()))
-            rel = ((q.grad[bi, hi, r].cpu().double() - dq_ref[0, 0, 0]).norm() / dq_ref.norm().clamp(min=1e-12)).item()
-            assert rel <= 2 * G_RTOL[dtype], (name, "dq", r, rel)  # one row: less averaging than a whole tensor
+            err = (q.grad[bi, hi, r].cpu().double() - dq_ref[0, 0, 0]).norm().item()
+            # one row: less averaging than a whole tensor; the absolute term covers rows whose exact gradient is 0
+            assert err <= 2 * G_RTOL[dtype] * dq_ref.norm().item() + 2e-2, (name, "dq", r, err)
     # ---- dK / dV on sampled key rows
     keys = torch.cat([torch.tensor([0, 127, 128, L - 1]), torch.randint(0, L, (12,), generator=gen)]).unique()
     bi, hi = B - 1, 0
@@ -96,8 +97,8 @@ def test_sampled_rows_and_identities(name):
         ds = p * (dos @ vv - (os_ * dos).sum(-1))
         dk_ref = (ds @ qs) * (D ** -0.5)
         for nm, mine, ref in (("dv", v.grad[bi, hi, kk], dv_ref), ("dk", k.grad[bi, hi, kk], dk_ref)):
-            rel = ((mine.cpu().double() - ref).norm() / ref.norm().clamp(min=1e-12)).item()
-            assert rel <= 3 * G_RTOL[dtype], (name, nm, kk, rel)
+            err = (mine.cpu().double() - ref).norm().item()
+            assert err <= 3 * G_RTOL[dtype] * ref.norm().item() + 2e-2, (name, nm, kk, err)
     # ---- checksum identity: sum over keys of dV equals sum over queries of dO
     lhs = v.grad.double().sum(dim=2)
     rhs = do.double().sum(dim=2)
