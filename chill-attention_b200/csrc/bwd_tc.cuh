@@ -111,7 +111,9 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int kChunkBytes = kTile * 128;
   const Geo& g = p.g;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  int hb, kt;
+  cta_order((int)blockIdx.x, g.B * g.Hkv, (g.Lk + kTile - 1) / kTile, hb, kt);  // first key tile = most query tiles (causal)
+  const int hk = hb % g.Hkv, b = hb / g.Hkv;
   const int G = g.H / g.Hkv;
   const int kb = kt * kTile;
   const int kg0 = kb + g.k_off;
@@ -414,8 +416,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr int kChunkBytes = kTile * 128;
   const Geo& g = p.g;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_qt_total = (g.Lq + kTile - 1) / kTile;
+  int hb, rank;
+  cta_order((int)blockIdx.x, g.B * g.H, n_qt_total, hb, rank);
+  const int qt = n_qt_total - 1 - rank;
+  const int h = hb % g.H, b = hb / g.H;
   const int hk = h / (g.H / g.Hkv);
   const int qb = qt * kTile;
   const int qg0 = qb + g.q_off;
@@ -677,13 +682,13 @@ int launch_bwd_one(const CUtensorMap* maps, const BwdTcParams& p, cudaStream_t s
   const Geo& g = p.g;
   // maps: 0 Q, 1 K, 2 V, 3 dO, 4 dQ, 5 dK, 6 dV
   if (p.which & 1) {
-    dim3 gk((g.Lk + kTile - 1) / kTile, g.Hkv, g.B);
+    dim3 gk((unsigned)(((g.Lk + kTile - 1) / kTile) * g.Hkv * g.B), 1, 1);
     kdkdv<<<gk, kBwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[5], maps[6], p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
   }
   if (p.which & 2) {
-    dim3 gq((g.Lq + kTile - 1) / kTile, g.H, g.B);
+    dim3 gq((unsigned)(((g.Lq + kTile - 1) / kTile) * g.H * g.B), 1, 1);
     kdq<<<gq, kBwdThreads, smem_dq, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   }
   return (int)cudaGetLastError();

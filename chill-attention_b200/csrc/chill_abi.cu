@@ -211,7 +211,7 @@ static int fwd_tc(const chill_fwd_args& a, cudaStream_t st) {
   p.o_sb = a.o_strides[0]; p.o_sh = a.o_strides[1]; p.o_sl = a.o_strides[2];
   p.status = device_status_ptr();
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
-  dim3 grid((s.Lq + tc::kTile - 1) / tc::kTile, s.H, s.B);
+  dim3 grid((unsigned)(((s.Lq + tc::kTile - 1) / tc::kTile) * s.H * s.B), 1, 1);
   int e = 0;
   CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_fwd<MaskT>(s.dtype, s.D, maps, p, grid, st)))
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "fwd_tc launch");
