@@ -77,6 +77,125 @@ struct FwdSmem {
 // Status codes recorded by bounded waits (1xx = forward).
 enum : int { kStProducer = 101, kStMma = 102, kStSoftmax = 103, kStEpilogue = 104 };
 
+// Online-softmax step of one thread (= one query row) for one 128-key tile: reads the row of S from
+// TMEM, updates the running maximum / sum, rescales the O accumulator in TMEM when needed and writes the
+// 16-bit P row back over S.  `first` = first key tile of this row (no O to rescale yet).
+template <typename T, int D, class M>
+__device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_sel, bool first, bool full, int klim,
+                                             int qg, int kg0, int n, const MaskArgs& margs, float c, float& m_used,
+                                             float& l) {
+  // One pass over the row: all 128 scores of this thread's row come into registers, the maximum
+  // is taken with 3-input max on four independent chains, and exponentials, row sum and the
+  // 16-bit packing run on pairs (packed fp32 FMA / ADD).  Full tiles skip the mask arithmetic
+  // (separate copy of the body, so nothing is if-converted into the fast path).
+  uint32_t sreg[kTile];
+#pragma unroll
+  for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tS + lane_sel + q4 * 32, sreg + q4 * 32);
+  tmem_wait_ld();
+  if (!full) {
+#pragma unroll
+    for (int cidx = 0; cidx < kTile; ++cidx) {
+      const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, margs);
+      sreg[cidx] = vis ? sreg[cidx] : 0xff800000u;  // -inf
+    }
+  }
+  float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+#pragma unroll
+  for (int i = 0; i < kTile; i += 8) {
+    mx0 = fmax3(mx0, __uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1]));
+    mx1 = fmax3(mx1, __uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3]));
+    mx2 = fmax3(mx2, __uint_as_float(sreg[i + 4]), __uint_as_float(sreg[i + 5]));
+    mx3 = fmax3(mx3, __uint_as_float(sreg[i + 6]), __uint_as_float(sreg[i + 7]));
+  }
+  const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // c > 0 (checked by the host)
+  const float m_cand = fmaxf(m_used, m_tile);
+  if (first) {
+    m_used = m_cand;
+  } else {
+    const bool need = (m_cand - m_used) > kRescaleThreshold;  // false when both are -inf
+    if (__any_sync(0xffffffffu, need)) {
+      const float alpha = (m_cand == -CUDART_INF_F) ? 1.f : ex2(m_used - m_cand);
+      l *= alpha;
+      m_used = m_cand;
+#pragma unroll 1
+      for (int q4 = 0; q4 < D / 16; ++q4) {
+        uint32_t oreg[16];
+        tmem_ld16(tO + lane_sel + q4 * 16, oreg);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+        tmem_st16(tO + lane_sel + q4 * 16, oreg);
+      }
+    }
+  }
+  const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
+  const uint64_t c2 = pk2(c, c), nm2 = pk2(-m_safe, -m_safe);
+  uint64_t l0 = 0ull, l1 = 0ull;  // two packed partial row sums (+0.0f, +0.0f)
+#pragma unroll
+  for (int i = 0; i < kTile / 2; i += 2) {
+    // two pairs per step; a fixed share of the pairs takes the polynomial 2^x (FMA pipe), the rest MUFU
+    const uint64_t e0 = ex2_pair(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nm2),
+                                 (i % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
+    const uint64_t e1 = ex2_pair(ffma2(pk2u(sreg[2 * i + 2], sreg[2 * i + 3]), c2, nm2),
+                                 ((i + 1) % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
+    l0 = fadd2(l0, e0);
+    l1 = fadd2(l1, e1);
+    float p0, p1, p2, p3;
+    upk2(e0, p0, p1);
+    upk2(e1, p2, p3);
+    sreg[i] = pack2<T>(p0, p1);      // 16-bit P pair i overwrites a slot already consumed (i <= 2i)
+    sreg[i + 1] = pack2<T>(p2, p3);
+  }
+  {
+    float a0, a1, a2, a3;
+    upk2(l0, a0, a1);
+    upk2(l1, a2, a3);
+    l += (a0 + a1) + (a2 + a3);
+  }
+  tmem_st32(tS + lane_sel, sreg);
+  tmem_st32(tS + lane_sel + 32, sreg + 32);
+}
+
+// Normalise this thread's O row, convert to 16 bits and stage it in the 128B-swizzled TMA box layout;
+// also writes the row's LSE.  `have` = the accumulator holds data (at least one key tile was processed).
+template <typename T, int D>
+__device__ __forceinline__ void stage_output_row(uint8_t* sO, uint32_t tO, uint32_t lane_sel, int r, bool have,
+                                                 bool row_valid, float l, float m_used, float* lse_ptr) {
+  const float l_safe = (l == 0.f) ? 1.f : l;
+  const float inv = 1.f / l_safe;
+#pragma unroll
+  for (int q4 = 0; q4 < D / 32; ++q4) {
+    uint32_t oreg[32];
+    if (have) {
+      tmem_ld32(tO + lane_sel + q4 * 32, oreg);
+      tmem_wait_ld();
+    }
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float a = 0.f, bb = 0.f;
+      if (have && row_valid && l != 0.f) {
+        a = __uint_as_float(oreg[2 * i]) * inv;
+        bb = __uint_as_float(oreg[2 * i + 1]) * inv;
+      }
+      packed[i] = pack2<T>(a, bb);
+    }
+    // 32 channels = 64 bytes = four 16-byte units of the row's 128-byte line in chunk (q4 / 2)
+    uint8_t* line = sO + (q4 / 2) * (kTile * 128) + r * 128;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int unit = ((q4 % 2) * 4 + u) ^ (r & 7);
+      *reinterpret_cast<uint4*>(line + unit * 16) =
+          make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+    }
+  }
+  if (lse_ptr != nullptr) {
+    float v = 0.f;
+    if (row_valid) v = (l == 0.f) ? -CUDART_INF_F : m_used + lg2(l);
+    *lse_ptr = v;
+  }
+}
+
 template <typename T, int D, class M, int NSTAGE>
 __global__ void __launch_bounds__(kFwdThreads, 2)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -253,76 +372,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
                         kt * kTile + kTile <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * kTile);  // columns >= klim do not exist
-      // One pass over the row: all 128 scores of this thread's row come into registers, the maximum
-      // is taken with 3-input max on four independent chains, and exponentials, row sum and the
-      // 16-bit packing run on pairs (packed fp32 FMA / ADD).  Full tiles skip the mask arithmetic
-      // (separate copy of the body, so nothing is if-converted into the fast path).
-      uint32_t sreg[kTile];
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tS + lane_sel + q4 * 32, sreg + q4 * 32);
-      tmem_wait_ld();
-      if (!full) {
-#pragma unroll
-        for (int cidx = 0; cidx < kTile; ++cidx) {
-          const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, g.margs);
-          sreg[cidx] = vis ? sreg[cidx] : 0xff800000u;  // -inf
-        }
-      }
-      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
-#pragma unroll
-      for (int i = 0; i < kTile; i += 8) {
-        mx0 = fmax3(mx0, __uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1]));
-        mx1 = fmax3(mx1, __uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3]));
-        mx2 = fmax3(mx2, __uint_as_float(sreg[i + 4]), __uint_as_float(sreg[i + 5]));
-        mx3 = fmax3(mx3, __uint_as_float(sreg[i + 6]), __uint_as_float(sreg[i + 7]));
-      }
-      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;  // c > 0 (checked by the host)
-      const float m_cand = fmaxf(m_used, m_tile);
-      if (j == 0) {
-        m_used = m_cand;
-      } else {
-        const bool need = (m_cand - m_used) > kRescaleThreshold;  // false when both are -inf
-        if (__any_sync(0xffffffffu, need)) {
-          const float alpha = (m_cand == -CUDART_INF_F) ? 1.f : ex2(m_used - m_cand);
-          l *= alpha;
-          m_used = m_cand;
-#pragma unroll 1
-          for (int q4 = 0; q4 < D / 16; ++q4) {
-            uint32_t oreg[16];
-            tmem_ld16(tO + lane_sel + q4 * 16, oreg);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-            tmem_st16(tO + lane_sel + q4 * 16, oreg);
-          }
-        }
-      }
-      const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
-      const uint64_t c2 = pk2(c, c), nm2 = pk2(-m_safe, -m_safe);
-      uint64_t l0 = 0ull, l1 = 0ull;  // two packed partial row sums (+0.0f, +0.0f)
-#pragma unroll
-      for (int i = 0; i < kTile / 2; i += 2) {
-        // two pairs per step; a fixed share of the pairs takes the polynomial 2^x (FMA pipe), the rest MUFU
-        const uint64_t e0 = ex2_pair(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nm2),
-                                     (i % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
-        const uint64_t e1 = ex2_pair(ffma2(pk2u(sreg[2 * i + 2], sreg[2 * i + 3]), c2, nm2),
-                                     ((i + 1) % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
-        l0 = fadd2(l0, e0);
-        l1 = fadd2(l1, e1);
-        float p0, p1, p2, p3;
-        upk2(e0, p0, p1);
-        upk2(e1, p2, p3);
-        sreg[i] = pack2<T>(p0, p1);      // 16-bit P pair i overwrites a slot already consumed (i <= 2i)
-        sreg[i + 1] = pack2<T>(p2, p3);
-      }
-      {
-        float a0, a1, a2, a3;
-        upk2(l0, a0, a1);
-        upk2(l1, a2, a3);
-        l += (a0 + a1) + (a2 + a3);
-      }
-      tmem_st32(tS + lane_sel, sreg);
-      tmem_st32(tS + lane_sel + 32, sreg + 32);
+      softmax_tile<T, D, M>(tS, tO, lane_sel, j == 0, full, klim, qg, kg0, n, g.margs, c, m_used, l);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -334,40 +384,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     const bool row_valid = qg < n;
-    const float l_safe = (l == 0.f) ? 1.f : l;
-    const float inv = 1.f / l_safe;
-    uint8_t* sO = gen_base + L::kQ;
-#pragma unroll
-    for (int q4 = 0; q4 < D / 32; ++q4) {
-      uint32_t oreg[32];
-      if (n_tiles > 0 && ok) {
-        tmem_ld32(tO + lane_sel + q4 * 32, oreg);
-        tmem_wait_ld();
-      }
-      uint32_t packed[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float a = 0.f, bb = 0.f;
-        if (n_tiles > 0 && ok && row_valid && l != 0.f) {
-          a = __uint_as_float(oreg[2 * i]) * inv;
-          bb = __uint_as_float(oreg[2 * i + 1]) * inv;
-        }
-        packed[i] = pack2<T>(a, bb);
-      }
-      // 32 channels = 64 bytes = four 16-byte units of the row's 128-byte line in chunk (q4 / 2)
-      uint8_t* line = sO + (q4 / 2) * kChunkBytes + r * 128;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int unit = ((q4 % 2) * 4 + u) ^ (r & 7);
-        *reinterpret_cast<uint4*>(line + unit * 16) =
-            make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
-      }
-    }
-    if (p.lse != nullptr && qb + r < g.Lq) {
-      float v = 0.f;
-      if (row_valid) v = (l == 0.f) ? -CUDART_INF_F : m_used + lg2(l);
-      p.lse[b * p.lse_sb + h * p.lse_sh + (qb + r) * p.lse_sl] = v;
-    }
+    stage_output_row<T, D>(gen_base + L::kQ, tO, lane_sel, r, n_tiles > 0 && ok, row_valid, l, m_used,
+                           (p.lse != nullptr && qb + r < g.Lq) ? p.lse + b * p.lse_sb + h * p.lse_sh + (qb + r) * p.lse_sl
+                                                                : nullptr);
     fence_proxy_async_smem();
     named_bar_sync(1, 128);
     if (threadIdx.x == 0) {
