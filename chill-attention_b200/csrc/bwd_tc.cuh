@@ -101,6 +101,15 @@ __device__ __forceinline__ void stage_row32(uint8_t* tile, int r, int q4, const 
 }
 
 // =========================================================================== dK / dV
+// TMEM: S^T (128 columns, overlaid by the 16-bit P^T), dP^T (128, overlaid by dS^T), dV, dK: 512 columns,
+// every MMA at N = 128.  Tensor-core order in steady state (u = query tile):
+//     dV += P^T(u) dO(u)      needs P^T(u)
+//     S^T(u+1) = K Q(u+1)^T
+//     dK += dS^T(u) Q(u)      needs dS^T(u)
+//     dP^T(u+1) = V dO(u+1)^T
+// The compute warps work in two steps per tile: the exponentials P^T = 2^(S^T c - LSE) as soon as S^T is
+// there (while the tensor cores run dK(u-1) and dP^T(u)), then dS^T = P^T (dP^T - delta) once dP^T has
+// landed (while dV(u) and S^T(u+1) run).  The MUFU-heavy step is thereby off the tensor cores' critical path.
 template <typename T, int D, class M>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -147,10 +156,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t sK = base + L::kFixA, sV = base + L::kFixB, sRing = base + L::kRing;
-  float* rows_s = reinterpret_cast<float*>(gen_base + L::kRows);  // [warp][0: lse, 1: delta][64]
+  float* rows_s = reinterpret_cast<float*>(gen_base + L::kRows);  // [warp][0: -lse, 1: -delta][64]
   const uint32_t bars = base + L::kBars;
-  // s_full / p_full: one barrier per score buffer (index = half & 1)
-  const uint32_t bar_kv_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_p_full = bars + 32;
+  const uint32_t bar_kv_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_dp_full = bars + 24,
+                 bar_p_full = bars + 32, bar_ds_full = bars + 40;
   const uint32_t bar_ring_full = bars + 48, bar_ring_empty = bar_ring_full + 8 * L::kStages;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
@@ -160,10 +169,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     *abort_flag = 0;
     mbar_init(bar_kv_full, 1);
     mbar_init(bar_acc_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_p_full + 8 * i, kBwdComputeThreads / 32);
-    }
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_dp_full, 1);
+    mbar_init(bar_p_full, kBwdComputeThreads / 32);
+    mbar_init(bar_ds_full, kBwdComputeThreads / 32);
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(bar_ring_full + 8 * s, 1);
       mbar_init(bar_ring_empty + 8 * s, 1);
@@ -214,148 +223,177 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp == 9) {
     // ----------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc<T>(kTile, 64, false, false);
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
       constexpr uint32_t idesc_acc = make_idesc<T>(kTile, D, false, true);
-      const int n_half = 2 * n_it;
-      bool ok = mbar_wait(bar_kv_full, 0, guard, kStBwdMma);
-      // S^T / dP^T of half u (64 queries) into score buffer u & 1
       constexpr uint32_t hi_k = desc_hi_sw128(1024);
       const uint32_t k_lo = desc_lo_sw128(sK, 16), v_lo = desc_lo_sw128(sV, 16);
-      auto issue_scores = [&](int u) -> bool {
-        const int it = u >> 1, hf = u & 1, s = it % L::kStages;
-        const uint32_t sQ = sRing + s * 2 * L::kTileBytes, sdO = sQ + L::kTileBytes;
-        const uint32_t q_lo = desc_lo_sw128(sQ + hf * 8192, 16), do_lo = desc_lo_sw128(sdO + hf * 8192, 16);
-        if (hf == 0) {
-          if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)(it / L::kStages) & 1u, guard, kStBwdMma)) return false;
-          tc_fence_after();
-        }
+      bool ok = mbar_wait(bar_kv_full, 0, guard, kStBwdMma);
+      auto stage_q = [&](int it) { return sRing + (it % L::kStages) * 2 * L::kTileBytes; };
+      auto issue_s = [&](int it) -> bool {  // S^T(it) = K Q^T; first user of ring stage `it`
+        const int s = it % L::kStages;
+        if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)(it / L::kStages) & 1u, guard, kStBwdMma)) return false;
+        tc_fence_after();
+        const uint32_t q_lo = desc_lo_sw128(stage_q(it), 16);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)  // S^T = K Q^T   (B = 64 query rows of the Q tile)
-          mma_ss_lh(tSt + hf * 64, k_lo + kmajor_step(kk), q_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)  // dP^T = V dO^T
-          mma_ss_lh(tdPt + hf * 64, v_lo + kmajor_step(kk), do_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
-        mma_commit(bar_s_full + 8 * hf);
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss_lh(tSt, k_lo + kmajor_step(kk), q_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
+        mma_commit(bar_s_full);
         return true;
       };
-      if (ok) ok = issue_scores(0);
-      for (int u = 0; u < n_half && ok; ++u) {
-        const int it = u >> 1, hf = u & 1, s = it % L::kStages;
-        const uint32_t sQ = sRing + s * 2 * L::kTileBytes, sdO = sQ + L::kTileBytes;
-        // MN-major B operands: the half's 64 query rows start 8 KB into each 64-channel block
-        const uint32_t qmn_lo = desc_lo_sw128(sQ + hf * 8192, kChunkBytes), domn_lo = desc_lo_sw128(sdO + hf * 8192, kChunkBytes);
-        if (u + 1 < n_half) {
-          ok = issue_scores(u + 1);  // tensor cores stay busy while half u is exponentiated
-          if (!ok) break;
-        }
-        ok = mbar_wait(bar_p_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStBwdMma);
+      auto issue_dp = [&](int it) {  // dP^T(it) = V dO^T
+        const uint32_t do_lo = desc_lo_sw128(stage_q(it) + L::kTileBytes, 16);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss_lh(tdPt, v_lo + kmajor_step(kk), do_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
+        mma_commit(bar_dp_full);
+      };
+      if (ok) ok = issue_s(0);
+      if (ok) issue_dp(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint32_t par = (uint32_t)it & 1u;
+        const uint32_t qmn_lo = desc_lo_sw128(stage_q(it), kChunkBytes);
+        const uint32_t domn_lo = desc_lo_sw128(stage_q(it) + L::kTileBytes, kChunkBytes);
+        ok = mbar_wait(bar_p_full, par, guard, kStBwdMma);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {  // dV += P^T dO ; dK += dS^T Q   (16 of the half's 64 queries per step)
-          const uint32_t acol = hf * 64 + (kk / 2) * 32 + (kk % 2) * 8;
-          mma_ts_lh(tdV, tSt + acol, domn_lo + kk * 128, hi_k, idesc_acc, (u > 0 || kk > 0));
-          mma_ts_lh(tdK, tdPt + acol, qmn_lo + kk * 128, hi_k, idesc_acc, (u > 0 || kk > 0));
+        for (int kk = 0; kk < kTile / 16; ++kk)  // dV += P^T dO   (16 queries per step)
+          mma_ts_lh(tdV, tSt + (kk / 4) * 64 + (kk % 4) * 8, domn_lo + kk * 128, hi_k, idesc_acc, (it > 0 || kk > 0));
+        if (it + 1 < n_it) {
+          ok = issue_s(it + 1);  // overwrites P^T(it) only after dV(it) has read it (MMAs complete in order)
+          if (!ok) break;
         }
-        if (hf == 1) mma_commit(bar_ring_empty + 8 * s);
+        ok = mbar_wait(bar_ds_full, par, guard, kStBwdMma);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)  // dK += dS^T Q
+          mma_ts_lh(tdK, tdPt + (kk / 4) * 64 + (kk % 4) * 8, qmn_lo + kk * 128, hi_k, idesc_acc, (it > 0 || kk > 0));
+        mma_commit(bar_ring_empty + 8 * (it % L::kStages));
+        if (it + 1 < n_it) issue_dp(it + 1);
       }
       if (ok) mma_commit(bar_acc_full);
     }
   } else {
     // ------------------------------------------------------------------- compute warps
-    const int wg = warp >> 2;                       // which 32 columns of a half
+    const int wg = warp >> 2;                       // column half: query columns [64 wg, 64 wg + 64)
     const int r = (warp & 3) * 32 + lane;           // key row inside the tile == TMEM lane
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const int cw0 = wg * 32;
+    const int c0 = wg * 64;
     const int kg = kg0 + r;
     const bool key_ok = kg < n && kb + r < g.Lk;
     const float c = g.scale * kLog2e;
+    const uint64_t c2 = pk2(c, c);
     const int t = threadIdx.x;  // 0..255
-    float* slot = rows_s + warp * 128;  // warp-private: [0,32) LSE, [64,96) delta of this warp's columns
+    float* slot = rows_s + warp * 128;  // warp-private: [0,64) -LSE, [64,128) -delta of this warp's columns
     bool ok = true;
-    const int n_half = 2 * n_it;
-    // -LSE and -delta of this lane's query column of half u; fetched one half ahead so the global
-    // load latency hides behind the exponentials of the current half.
-    auto fetch_rows = [&](int u, float& nl, float& nd) {
-      const int it = u >> 1, hf = u & 1;
+    // -LSE / -delta of this lane's two query columns of tile `it`, fetched one tile ahead
+    auto fetch_rows = [&](int it, float* nl, float* nd) {
       const int h = hk * G + it / n_qt;
-      const int qrow = (qt_lo + it % n_qt) * kTile + hf * 64 + cw0 + lane;
-      nl = 0.f;
-      nd = 0.f;
-      if (qrow < g.Lq) {
-        const float lv = p.lse[b * p.lse_sb + h * p.lse_sh + qrow * p.lse_sl];
-        nl = (lv == -CUDART_INF_F) ? 0.f : -lv;
-        nd = -p.delta[((long long)b * g.H + h) * g.Lq + qrow];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int qrow = (qt_lo + it % n_qt) * kTile + c0 + e * 32 + lane;
+        nl[e] = 0.f;
+        nd[e] = 0.f;
+        if (qrow < g.Lq) {
+          const float lv = p.lse[b * p.lse_sb + h * p.lse_sh + qrow * p.lse_sl];
+          nl[e] = (lv == -CUDART_INF_F) ? 0.f : -lv;
+          nd[e] = -p.delta[((long long)b * g.H + h) * g.Lq + qrow];
+        }
       }
     };
-    float nl_next, nd_next;
+    float nl_next[2], nd_next[2];
     fetch_rows(0, nl_next, nd_next);
-    for (int u = 0; u < n_half; ++u) {
-      const int it = u >> 1, hf = u & 1;
+    for (int it = 0; it < n_it; ++it) {
+      const uint32_t par = (uint32_t)it & 1u;
       const int qi = qt_lo + it % n_qt;
       const int qg0 = qi * kTile + g.q_off;
-      const int cbase = hf * 64 + cw0;  // first of this warp's 32 query columns inside the tile
       __syncwarp();
-      slot[lane] = nl_next;  // negated: they enter the packed FMA / ADD as addends
-      slot[64 + lane] = nd_next;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        slot[e * 32 + lane] = nl_next[e];
+        slot[64 + e * 32 + lane] = nd_next[e];
+      }
       __syncwarp();
-      if (u + 1 < n_half) fetch_rows(u + 1, nl_next, nd_next);
-      ok = mbar_wait(bar_s_full + 8 * hf, (uint32_t)(u >> 1) & 1u, guard, kStBwdCompute);
-      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
-      if (!ok) break;
-      tc_fence_after();
+      if (it + 1 < n_it) fetch_rows(it + 1, nl_next, nd_next);
       const bool full = M::kHasQFullRange && qg0 >= full_lo && qg0 + kTile <= full_hi && qg0 + kTile <= n &&
                         qi * kTile + kTile <= g.Lq && kg0 + kTile <= n && kb + kTile <= g.Lk;
       const int qlim = imin(n - qg0, g.Lq - qi * kTile);
-      uint32_t sreg[32], dpreg[32], preg[16], dsreg[16];
-      tmem_ld32(tSt + lane_sel + cbase, sreg);
-      tmem_ld32(tdPt + lane_sel + cbase, dpreg);
-      tmem_wait_ld();
-      // Packed fp32 pairs throughout; the slot holds -LSE and -delta so both enter as FMA / ADD addends.
-      const uint64_t c2 = pk2(c, c);
-      auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
-        constexpr bool kMasked = decltype(masked_tag)::value;
+
+      // ---- step 1: P^T = 2^(S^T c - LSE), masked; 16-bit copy to TMEM for the dV GEMM, kept packed in registers
+      ok = mbar_wait(bar_s_full, par, guard, kStBwdCompute);
+      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t preg[32];
+      {
+        uint32_t sreg[64];
+        tmem_ld32(tSt + lane_sel + c0, sreg);
+        tmem_ld32(tSt + lane_sel + c0 + 32, sreg + 32);
+        tmem_wait_ld();
+        auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
+          constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {  // four query columns per step
-          const float4 nl4 = reinterpret_cast<const float4*>(slot)[j];
-          const float4 nd4 = reinterpret_cast<const float4*>(slot + 64)[j];
-          float p0, p1, p2, p3, d0, d1, d2, d3;
-          upk2(ex2_pair(ffma2(pk2u(sreg[4 * j], sreg[4 * j + 1]), c2, pk2(nl4.x, nl4.y)),
-                        ((2 * j) % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM), p0, p1);
-          upk2(ex2_pair(ffma2(pk2u(sreg[4 * j + 2], sreg[4 * j + 3]), c2, pk2(nl4.z, nl4.w)),
-                        ((2 * j + 1) % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM), p2, p3);
-          if (kMasked) {
-            const int cq = cbase + 4 * j;
-            p0 = (key_ok && cq < qlim && M::mask(qg0 + cq, kg, n, g.margs)) ? p0 : 0.f;
-            p1 = (key_ok && cq + 1 < qlim && M::mask(qg0 + cq + 1, kg, n, g.margs)) ? p1 : 0.f;
-            p2 = (key_ok && cq + 2 < qlim && M::mask(qg0 + cq + 2, kg, n, g.margs)) ? p2 : 0.f;
-            p3 = (key_ok && cq + 3 < qlim && M::mask(qg0 + cq + 3, kg, n, g.margs)) ? p3 : 0.f;
+          for (int j = 0; j < 16; ++j) {  // four query columns per step
+            const float4 nl4 = reinterpret_cast<const float4*>(slot)[j];
+            float p0, p1, p2, p3;
+            upk2(ex2_pair(ffma2(pk2u(sreg[4 * j], sreg[4 * j + 1]), c2, pk2(nl4.x, nl4.y)),
+                          ((2 * j) % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM), p0, p1);
+            upk2(ex2_pair(ffma2(pk2u(sreg[4 * j + 2], sreg[4 * j + 3]), c2, pk2(nl4.z, nl4.w)),
+                          ((2 * j + 1) % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM), p2, p3);
+            if (kMasked) {
+              const int cq = c0 + 4 * j;
+              p0 = (key_ok && cq < qlim && M::mask(qg0 + cq, kg, n, g.margs)) ? p0 : 0.f;
+              p1 = (key_ok && cq + 1 < qlim && M::mask(qg0 + cq + 1, kg, n, g.margs)) ? p1 : 0.f;
+              p2 = (key_ok && cq + 2 < qlim && M::mask(qg0 + cq + 2, kg, n, g.margs)) ? p2 : 0.f;
+              p3 = (key_ok && cq + 3 < qlim && M::mask(qg0 + cq + 3, kg, n, g.margs)) ? p3 : 0.f;
+            }
+            preg[2 * j] = pack2<T>(p0, p1);
+            preg[2 * j + 1] = pack2<T>(p2, p3);
           }
-          upk2(fmul2(pk2(p0, p1), fadd2(pk2u(dpreg[4 * j], dpreg[4 * j + 1]), pk2(nd4.x, nd4.y))), d0, d1);
-          upk2(fmul2(pk2(p2, p3), fadd2(pk2u(dpreg[4 * j + 2], dpreg[4 * j + 3]), pk2(nd4.z, nd4.w))), d2, d3);
-          preg[2 * j] = pack2<T>(p0, p1);
-          preg[2 * j + 1] = pack2<T>(p2, p3);
-          dsreg[2 * j] = pack2<T>(d0, d1);
-          dsreg[2 * j + 1] = pack2<T>(d2, d3);
-        }
-      };
-      if (full) body(std::false_type{});
-      else body(std::true_type{});
-      // 16-bit P^T / dS^T over the fp32 columns this warp just consumed
-      tmem_st16(tSt + lane_sel + cbase, preg);
-      tmem_st16(tdPt + lane_sel + cbase, dsreg);
+        };
+        if (full) body(std::false_type{});
+        else body(std::true_type{});
+      }
+      tmem_st32(tSt + lane_sel + c0, preg);  // over the first half of the fp32 columns this warp just consumed
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full + 8 * hf);  // one arrival per compute warp
+      if (lane == 0) mbar_arrive(bar_p_full);
+
+      // ---- step 2: dS^T = P^T (dP^T - delta) with the rounded P^T the dV GEMM uses
+      ok = mbar_wait(bar_dp_full, par, guard, kStBwdCompute);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        uint32_t dpreg[64];
+        tmem_ld32(tdPt + lane_sel + c0, dpreg);
+        tmem_ld32(tdPt + lane_sel + c0 + 32, dpreg + 32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float4 nd4 = reinterpret_cast<const float4*>(slot + 64)[j];
+          float p0, p1, p2, p3, d0, d1, d2, d3;
+          unpack2<T>(preg[2 * j], p0, p1);
+          unpack2<T>(preg[2 * j + 1], p2, p3);
+          upk2(fmul2(pk2(p0, p1), fadd2(pk2u(dpreg[4 * j], dpreg[4 * j + 1]), pk2(nd4.x, nd4.y))), d0, d1);
+          upk2(fmul2(pk2(p2, p3), fadd2(pk2u(dpreg[4 * j + 2], dpreg[4 * j + 3]), pk2(nd4.z, nd4.w))), d2, d3);
+          preg[2 * j] = pack2<T>(d0, d1);
+          preg[2 * j + 1] = pack2<T>(d2, d3);
+        }
+      }
+      tmem_st32(tdPt + lane_sel + c0, preg);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ds_full);
     }
 
     // ---- epilogue: warps 0-3 store dV, warps 4-7 store dK * sm_scale (staging = ring stage 0)
     if (ok) ok = mbar_wait(bar_acc_full, 0, guard, kStBwdEpilogue);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
-    const int c0 = 0;
-    (void)c0;
     uint8_t* stage = gen_base + L::kRing + wg * L::kTileBytes;
     const uint32_t tacc = wg == 0 ? tdV : tdK;
     const float mul = wg == 0 ? 1.f : g.scale;
