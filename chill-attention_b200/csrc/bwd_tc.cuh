@@ -427,8 +427,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // 16-bit dS) and the dQ accumulator.  Every MMA runs at N = 128.  Tensor-core order per key tile u:
 //   dQ += dS(u) K(u)   (in two halves, each as soon as its 64 columns of dS are in TMEM)
 //   dP(u+1) = dO V(u+1)^T,   S(u+2) = Q K(u+2)^T
-// so the exponentials of tile u+1 overlap S(u+2) and the first half of the dQ GEMM.  K needs three
-// ring stages (S(u+2) is issued while K(u) is still read by the dQ GEMM), V two.
+// The compute warps take two steps per tile, like the dK/dV kernel: P = 2^(S c - LSE) as soon as S(u+1) is
+// there (it is issued a whole tile ahead, so this overlaps dQ(u) and dP(u+1)), then dS = P (dP - delta) when
+// dP(u+1) has landed.  K needs three ring stages (S(u+2) is issued while K(u) is still read by the dQ GEMM),
+// V two.
 template <int D>
 struct DqSmem {
   static constexpr int kTileBytes = kTile * D * 2;
@@ -438,7 +440,7 @@ struct DqSmem {
   static constexpr int kK = kdO + kTileBytes;
   static constexpr int kV = kK + kKStages * kTileBytes;
   static constexpr int kBars = kV + kVStages * kTileBytes;
-  static constexpr int kNumBars = 5 + 2 * kKStages + 2 * kVStages;
+  static constexpr int kNumBars = 7 + 2 * kKStages + 2 * kVStages;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;
@@ -489,8 +491,9 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t sQ = base + L::kQ, sdO = base + L::kdO, sKr = base + L::kK, sVr = base + L::kV;
   const uint32_t bars = base + L::kBars;
-  const uint32_t bar_q_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_p_full = bars + 24;  // p_full[2]
-  const uint32_t bar_k_full = bars + 40, bar_k_empty = bar_k_full + 8 * L::kKStages;
+  const uint32_t bar_q_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16 /* [2], per S buffer */,
+                 bar_p_full = bars + 32 /* [2], per column half */, bar_dp_full = bars + 48;
+  const uint32_t bar_k_full = bars + 56, bar_k_empty = bar_k_full + 8 * L::kKStages;
   const uint32_t bar_v_full = bar_k_empty + 8 * L::kKStages, bar_v_empty = bar_v_full + 8 * L::kVStages;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
@@ -501,6 +504,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(bar_q_full, 1);
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_s_full, 1);
+    mbar_init(bar_s_full + 8, 1);
+    mbar_init(bar_dp_full, 1);
     mbar_init(bar_p_full, kBwdComputeThreads / 32);
     mbar_init(bar_p_full + 8, kBwdComputeThreads / 32);
     for (int s = 0; s < L::kKStages; ++s) {
@@ -570,9 +575,10 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           mma_ss_lh(tS + (it & 1) * 128, q_lo + kmajor_step(kk), k_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
+        mma_commit(bar_s_full + 8 * (it & 1));
         return true;
       };
-      auto issue_dp = [&](int it) -> bool {  // dP(it) = dO V(it)^T; then both scores of tile `it` are complete
+      auto issue_dp = [&](int it) -> bool {  // dP(it) = dO V(it)^T
         const int vs = it % L::kVStages;
         if (!mbar_wait(bar_v_full + 8 * vs, (uint32_t)(it / L::kVStages) & 1u, guard, kStDqMma)) return false;
         tc_fence_after();
@@ -581,7 +587,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int kk = 0; kk < D / 16; ++kk)
           mma_ss_lh(tdP, do_lo + kmajor_step(kk), v_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0);
         mma_commit(bar_v_empty + 8 * vs);
-        mma_commit(bar_s_full);
+        mma_commit(bar_dp_full);
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -629,26 +635,27 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int it = 0; it < n_it; ++it) {
       const int kt = kt_lo + it;
       const int kg0 = kt * kTile + g.k_off;
-      ok = mbar_wait(bar_s_full, (uint32_t)it & 1u, guard, kStDqCompute);
-      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
-      if (!ok) break;
-      tc_fence_after();
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
                         kt * kTile + kTile <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * kTile);
       const uint32_t tSb = tS + (it & 1) * 128;
+      // ---- step 1: P = 2^(S c - LSE) as soon as S(it) is there (it was issued a tile ahead); kept packed
+      ok = mbar_wait(bar_s_full + 8 * (it & 1), (uint32_t)(it >> 1) & 1u, guard, kStDqCompute);
+      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t preg[2][16];
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int cbase = hf * 64 + wg * 32;  // this warp's 32 key columns of the half
-        uint32_t sreg[32], dpreg[32], dsreg[16];
+        uint32_t sreg[32];
         tmem_ld32(tSb + lane_sel + cbase, sreg);
-        tmem_ld32(tdP + lane_sel + cbase, dpreg);
         tmem_wait_ld();
         auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
           constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {  // packed fp32 pairs; lse = +inf on padded rows gives p = 0
-            float p0, p1, d0, d1;
+            float p0, p1;
             upk2(ex2_pair(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nl2), (i % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM),
                  p0, p1);
             if (kMasked) {
@@ -656,12 +663,30 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               p0 = (col < klim && M::mask(qg, kg0 + col, n, g.margs)) ? p0 : 0.f;
               p1 = (col + 1 < klim && M::mask(qg, kg0 + col + 1, n, g.margs)) ? p1 : 0.f;
             }
-            upk2(fmul2(pk2(p0, p1), fadd2(pk2u(dpreg[2 * i], dpreg[2 * i + 1]), nd2)), d0, d1);
-            dsreg[i] = pack2<T>(d0, d1);
+            preg[hf][i] = pack2<T>(p0, p1);
           }
         };
         if (full) body(std::false_type{});
         else body(std::true_type{});
+      }
+      // ---- step 2: dS = P (dP - delta) once dP(it) has landed; each half goes to the dQ GEMM as soon as it is stored
+      ok = mbar_wait(bar_dp_full, (uint32_t)it & 1u, guard, kStDqCompute);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int cbase = hf * 64 + wg * 32;
+        uint32_t dpreg[32], dsreg[16];
+        tmem_ld32(tdP + lane_sel + cbase, dpreg);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0, p1, d0, d1;
+          unpack2<T>(preg[hf][i], p0, p1);
+          upk2(fmul2(pk2(p0, p1), fadd2(pk2u(dpreg[2 * i], dpreg[2 * i + 1]), nd2)), d0, d1);
+          dsreg[i] = pack2<T>(d0, d1);
+        }
         tmem_st16(tdP + lane_sel + cbase, dsreg);  // 16-bit dS over the dP columns this warp just consumed
         tmem_wait_st();
         tc_fence_before();
