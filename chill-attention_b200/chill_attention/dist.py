@@ -63,17 +63,21 @@ def halo_sizes(mask: ChillMask, shard_len: int) -> tuple[int, int]:
     return left, right
 
 
-def exchange_halos(k_local, v_local, left: int, right: int, group=None):
-    """Receive the last ``left`` rows of rank-1 and the first ``right`` rows of rank+1.
+def _peer(group):
+    return (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
 
-    Returns (k_ext, v_ext, hl, hr): local rows with the received halos attached along the
-    position axis; hl/hr are the halo lengths actually present (0 at the sequence ends)."""
+
+def start_halo_exchange(k_local, v_local, left: int, right: int, group=None):
+    """Post the K/V halo sends and receives (asynchronous).  Returns (works, recv_left, recv_right, hl, hr):
+    ``recv_left`` = [2, B, H, hl, D] buffer for the last ``left`` rows of rank-1 (K then V), ``recv_right`` the
+    first ``right`` rows of rank+1; hl / hr are 0 at the ends of the sequence.  Wait on ``works`` before
+    reading the buffers."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     hl = left if rank > 0 else 0
     hr = right if rank < world - 1 else 0
     B, H, Ls, D = k_local.shape
     ops, recv_l, recv_r = [], None, None
-    peer = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
+    peer = _peer(group)
     if rank < world - 1 and left > 0:  # my tail is the right neighbour's left halo
         tail = torch.stack([k_local[:, :, Ls - left:], v_local[:, :, Ls - left:]]).contiguous()
         ops.append(dist.P2POp(dist.isend, tail, peer(rank + 1), group))
@@ -86,65 +90,52 @@ def exchange_halos(k_local, v_local, left: int, right: int, group=None):
     if hr > 0:
         recv_r = torch.empty((2, B, H, hr, D), dtype=k_local.dtype, device=k_local.device)
         ops.append(dist.P2POp(dist.irecv, recv_r, peer(rank + 1), group))
-    if ops:
-        for w in dist.batch_isend_irecv(ops):
-            w.wait()
-    k_ext = torch.empty((B, H, hl + Ls + hr, D), dtype=k_local.dtype, device=k_local.device)
-    v_ext = torch.empty_like(k_ext)
-    k_ext[:, :, hl:hl + Ls] = k_local
-    v_ext[:, :, hl:hl + Ls] = v_local
-    if hl > 0:
-        k_ext[:, :, :hl], v_ext[:, :, :hl] = recv_l[0], recv_l[1]
-    if hr > 0:
-        k_ext[:, :, hl + Ls:], v_ext[:, :, hl + Ls:] = recv_r[0], recv_r[1]
-    return k_ext, v_ext, hl, hr
+    works = dist.batch_isend_irecv(ops) if ops else []
+    return works, recv_l, recv_r, hl, hr
 
 
-def return_halo_grads(dk_ext, dv_ext, hl: int, hr: int, left: int, right: int, group=None):
-    """Send the gradient rows of the halo keys back to their owners and add what the neighbours
-    computed for this rank's own boundary rows.  Returns (dk_local, dv_local)."""
+def exchange_halo_grads(dk_halo_left, dk_halo_right, left: int, right: int, like, group=None):
+    """Send the dK/dV rows computed for halo keys back to their owners; receive what the neighbours
+    computed for this rank's boundary rows.  ``dk_halo_left`` / ``dk_halo_right``: [2, B, H, hl|hr, D] or None.
+    Returns (from_right, from_left): [2, B, H, left, D] to add to the last ``left`` local rows, and
+    [2, B, H, right, D] to add to the first ``right`` rows (None where there is no neighbour)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
-    Ls = dk_ext.shape[2] - hl - hr
-    dk = dk_ext[:, :, hl:hl + Ls].contiguous()
-    dv = dv_ext[:, :, hl:hl + Ls].contiguous()
-    ops, recv_from_right, recv_from_left = [], None, None
-    peer = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
-    B, H, _, D = dk.shape
-    if hl > 0:  # gradients of the left neighbour's tail
-        ops.append(dist.P2POp(dist.isend, torch.stack([dk_ext[:, :, :hl], dv_ext[:, :, :hl]]).contiguous(), peer(rank - 1), group))
-    if hr > 0:
-        ops.append(dist.P2POp(dist.isend, torch.stack([dk_ext[:, :, hl + Ls:], dv_ext[:, :, hl + Ls:]]).contiguous(), peer(rank + 1), group))
+    B, H, _, D = like.shape
+    ops, from_right, from_left = [], None, None
+    peer = _peer(group)
+    if dk_halo_left is not None:
+        ops.append(dist.P2POp(dist.isend, dk_halo_left.contiguous(), peer(rank - 1), group))
+    if dk_halo_right is not None:
+        ops.append(dist.P2POp(dist.isend, dk_halo_right.contiguous(), peer(rank + 1), group))
     if rank < world - 1 and left > 0:  # the right neighbour used my last `left` rows as its left halo
-        recv_from_right = torch.empty((2, B, H, left, D), dtype=dk.dtype, device=dk.device)
-        ops.append(dist.P2POp(dist.irecv, recv_from_right, peer(rank + 1), group))
+        from_right = torch.empty((2, B, H, left, D), dtype=like.dtype, device=like.device)
+        ops.append(dist.P2POp(dist.irecv, from_right, peer(rank + 1), group))
     if rank > 0 and right > 0:
-        recv_from_left = torch.empty((2, B, H, right, D), dtype=dk.dtype, device=dk.device)
-        ops.append(dist.P2POp(dist.irecv, recv_from_left, peer(rank - 1), group))
-    if ops:
-        for w in dist.batch_isend_irecv(ops):
-            w.wait()
-    if recv_from_right is not None:
-        dk[:, :, Ls - left:] += recv_from_right[0]
-        dv[:, :, Ls - left:] += recv_from_right[1]
-    if recv_from_left is not None:
-        dk[:, :, :right] += recv_from_left[0]
-        dv[:, :, :right] += recv_from_left[1]
-    return dk, dv
+        from_left = torch.empty((2, B, H, right, D), dtype=like.dtype, device=like.device)
+        ops.append(dist.P2POp(dist.irecv, from_left, peer(rank - 1), group))
+    for w in (dist.batch_isend_irecv(ops) if ops else []):
+        w.wait()
+    return from_right, from_left
 
 
 # ------------------------------------------------------------------ local kernels (C ABI)
-def cabi_local_forward(mask, q, k_ext, v_ext, q_offset, k_offset, seq_len, sm_scale):
+def cabi_local_forward(mask, q, k_ext, v_ext, q_offset, k_offset, seq_len, sm_scale, o=None, lse=None):
+    """O, LSE of local query rows against local key rows with global offsets.  ``o`` / ``lse`` may be views
+    of larger buffers (row slices); they are written in place."""
     lib, functor = _library_for(mask)
-    o = torch.empty_like(q, memory_format=torch.contiguous_format)
-    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+    if o is None:
+        o = torch.empty_like(q, memory_format=torch.contiguous_format)
+    if lse is None:
+        lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
     shape = _cabi.make_shape(q, k_ext, functor, mask.constargs, None, sm_scale, q_offset, k_offset, seq_len)
     _cabi.forward(lib, q, k_ext, v_ext, o, lse, shape)
     return o, lse
 
 
-def cabi_local_backward(mask, q, k_ext, v_ext, o, lse, do, q_offset, k_offset, seq_len, sm_scale):
+def cabi_local_backward(mask, q, k_ext, v_ext, o, lse, do, q_offset, k_offset, seq_len, sm_scale, dq=None):
     lib, functor = _library_for(mask)
-    dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+    if dq is None:
+        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
     dk = torch.empty_like(k_ext, memory_format=torch.contiguous_format)
     dv = torch.empty_like(v_ext, memory_format=torch.contiguous_format)
     delta = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
@@ -161,25 +152,117 @@ def _library_for(mask):
 
 
 # -------------------------------------------------------------------- sharded operator
+def _regions(Ls, hl, hr, left, right):
+    """Row ranges of a shard: boundary rows that need the left halo, interior rows that only see local keys,
+    boundary rows that need the right halo; and the local key rows each boundary part can see."""
+    bl = left if hl > 0 else 0
+    br = right if hr > 0 else 0
+    if bl + br > Ls:  # tiny shard: treat every row as boundary-left (keys = halo_left + local + halo_right)
+        return None
+    return {"bl": bl, "br": br, "kl_hi": min(Ls, bl + right), "kr_lo": max(0, Ls - br - left)}
+
+
+def _call_fwd(fn, o, lse, mask, q, k, v, q_off, k_off, seq_len, sm_scale):
+    """Run a local forward into the views ``o`` / ``lse`` (callbacks without out-parameters are copied)."""
+    try:
+        ro, rl = fn(mask, q, k, v, q_off, k_off, seq_len, sm_scale, o=o, lse=lse)
+    except TypeError:
+        ro, rl = fn(mask, q, k, v, q_off, k_off, seq_len, sm_scale)
+    if ro.data_ptr() != o.data_ptr():
+        o.copy_(ro)
+        lse.copy_(rl)
+
+
 class _SequenceShardedAttention(torch.autograd.Function):
+    """Forward: post the halo exchange, run the interior rows (which see local keys only) while it is in
+    flight, then the boundary rows against [halo | the few local rows they can see].  Backward mirrors it and
+    returns the halo keys' dK/dV to their owners.  No full-size copy of K/V is ever made."""
+
     @staticmethod
     def forward(ctx, q, k, v, mask, seq_len, sm_scale, group, local_forward, local_backward):
         rank = dist.get_rank(group)
-        Ls = q.shape[2]
+        B, H, Ls, D = q.shape
         left, right = halo_sizes(mask, Ls)
-        k_ext, v_ext, hl, hr = exchange_halos(k, v, left, right, group)
-        q_off, k_off = rank * Ls, rank * Ls - hl
-        o, lse = local_forward(mask, q, k_ext, v_ext, q_off, k_off, seq_len, sm_scale)
-        ctx.save_for_backward(q, k_ext, v_ext, o, lse)
-        ctx.cfg = (mask, seq_len, sm_scale, group, local_backward, hl, hr, left, right, q_off, k_off)
+        works, recv_l, recv_r, hl, hr = start_halo_exchange(k, v, left, right, group)
+        reg = _regions(Ls, hl, hr, left, right)
+        base = rank * Ls
+        o = torch.empty((B, H, Ls, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, H, Ls), dtype=torch.float32, device=q.device)
+        parts = []  # (row slice, k tensor, v tensor, k_offset, halo rows in front, halo rows behind)
+        if reg is not None:
+            bl, br = reg["bl"], reg["br"]
+            if Ls - br > bl:  # interior first: independent of the exchange
+                sl = slice(bl, Ls - br)
+                _call_fwd(local_forward, o[:, :, sl], lse[:, :, sl], mask, q[:, :, sl], k, v, base + bl, base, seq_len, sm_scale)
+                parts.append((sl, None, None, base, 0, 0))
+        for w in works:
+            w.wait()
+        if reg is None:
+            pieces_k = ([recv_l[0]] if hl else []) + [k] + ([recv_r[0]] if hr else [])
+            pieces_v = ([recv_l[1]] if hl else []) + [v] + ([recv_r[1]] if hr else [])
+            k_ext, v_ext = torch.cat(pieces_k, dim=2), torch.cat(pieces_v, dim=2)
+            _call_fwd(local_forward, o, lse, mask, q, k_ext, v_ext, base, base - hl, seq_len, sm_scale)
+            parts.append((slice(0, Ls), k_ext, v_ext, base - hl, hl, hr))
+        else:
+            if reg["bl"] > 0:
+                k_b = torch.cat([recv_l[0], k[:, :, :reg["kl_hi"]]], dim=2)
+                v_b = torch.cat([recv_l[1], v[:, :, :reg["kl_hi"]]], dim=2)
+                sl = slice(0, reg["bl"])
+                _call_fwd(local_forward, o[:, :, sl], lse[:, :, sl], mask, q[:, :, sl], k_b, v_b, base, base - hl, seq_len, sm_scale)
+                parts.append((sl, k_b, v_b, base - hl, hl, 0))
+            if reg["br"] > 0:
+                k_b = torch.cat([k[:, :, reg["kr_lo"]:], recv_r[0]], dim=2)
+                v_b = torch.cat([v[:, :, reg["kr_lo"]:], recv_r[1]], dim=2)
+                sl = slice(Ls - reg["br"], Ls)
+                _call_fwd(local_forward, o[:, :, sl], lse[:, :, sl], mask, q[:, :, sl], k_b, v_b, base + Ls - reg["br"],
+                          base + reg["kr_lo"], seq_len, sm_scale)
+                parts.append((sl, k_b, v_b, base + reg["kr_lo"], 0, hr))
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.parts = parts
+        ctx.cfg = (mask, seq_len, sm_scale, group, local_backward, hl, hr, left, right, base, reg)
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k_ext, v_ext, o, lse = ctx.saved_tensors
-        mask, seq_len, sm_scale, group, local_backward, hl, hr, left, right, q_off, k_off = ctx.cfg
-        dq, dk_ext, dv_ext = local_backward(mask, q, k_ext, v_ext, o, lse, do.contiguous(), q_off, k_off, seq_len, sm_scale)
-        dk, dv = return_halo_grads(dk_ext, dv_ext, hl, hr, left, right, group)
+        q, k, v, o, lse = ctx.saved_tensors
+        mask, seq_len, sm_scale, group, local_backward, hl, hr, left, right, base, reg = ctx.cfg
+        B, H, Ls, D = q.shape
+        do = do.contiguous()
+        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+        dk = dv = None
+        small = []  # (dk_part, dv_part, first local key row, halo rows in front, halo rows behind)
+        for sl, k_b, v_b, k_off, h_front, h_back in ctx.parts:
+            qs, os_, ls, dos = q[:, :, sl], o[:, :, sl], lse[:, :, sl], do[:, :, sl]
+            kk, vv = (k, v) if k_b is None else (k_b, v_b)
+            q_off = base + sl.start
+            try:
+                rdq, rdk, rdv = local_backward(mask, qs, kk, vv, os_, ls, dos, q_off, k_off, seq_len, sm_scale, dq=dq[:, :, sl])
+            except TypeError:
+                rdq, rdk, rdv = local_backward(mask, qs, kk, vv, os_, ls, dos, q_off, k_off, seq_len, sm_scale)
+            if rdq.data_ptr() != dq[:, :, sl].data_ptr():
+                dq[:, :, sl].copy_(rdq)
+            if k_b is None:  # interior: its dK/dV cover every local key row and become the result buffers
+                dk, dv = rdk, rdv
+            else:
+                small.append((rdk, rdv, k_off + h_front - base, h_front, h_back))
+        if dk is None:
+            dk, dv = torch.zeros_like(k, memory_format=torch.contiguous_format), torch.zeros_like(v, memory_format=torch.contiguous_format)
+        send_l = send_r = None
+        for rdk, rdv, row0, h_front, h_back in small:
+            n_local = rdk.shape[2] - h_front - h_back
+            dk[:, :, row0:row0 + n_local] += rdk[:, :, h_front:h_front + n_local]
+            dv[:, :, row0:row0 + n_local] += rdv[:, :, h_front:h_front + n_local]
+            if h_front:
+                send_l = torch.stack([rdk[:, :, :h_front], rdv[:, :, :h_front]])
+            if h_back:
+                send_r = torch.stack([rdk[:, :, h_front + n_local:], rdv[:, :, h_front + n_local:]])
+        from_right, from_left = exchange_halo_grads(send_l, send_r, left, right, dk, group)
+        if from_right is not None:
+            dk[:, :, Ls - left:] += from_right[0]
+            dv[:, :, Ls - left:] += from_right[1]
+        if from_left is not None:
+            dk[:, :, :right] += from_left[0]
+            dv[:, :, :right] += from_left[1]
         return dq, dk, dv, None, None, None, None, None, None
 
 

@@ -79,6 +79,7 @@ def _spawn(world, *a):
 
 @pytest.mark.parametrize("world", [2, 3])
 @pytest.mark.parametrize("mask", [("SlidingWindowChillMask", (10, 0)), ("SlidingWindowChillMask", (7, 5)),
+                                  ("SlidingWindowChillMask", (9, 8)),  # both boundaries overlap on a 16-row shard
                                   ("ChunkwiseChillMask", (6, 1))], ids=str)
 def test_sequence_sharded_equals_single_process(world, mask):
     _spawn(world, mask[0], mask[1], 48, None)
