@@ -55,7 +55,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum per (batch, head) unit from the ncu capture summarised in
 # profiles/c2s_causal_bf16_kernels_ncu.md (causal bf16 L=4096 D=128, 32 units per launch); traffic grows in
 # proportion to the units a launch processes, so a full launch = per-unit figure x B x H.
-NCU_DRAM_BYTES_PER_UNIT = {("c2", "fwd"): 117.4e6 / 32, ("c2", "dkdv"): 177.8e6 / 32, ("c2", "dq"): 158.1e6 / 32}
+NCU_DRAM_BYTES_PER_UNIT = {("c2", "fwd"): 117.9e6 / 32, ("c2", "dkdv"): 176.5e6 / 32, ("c2", "dq"): 156.1e6 / 32}
 
 WORKLOADS = {
     # name: (mask class, mask args, dtype, B, H, L, D)
