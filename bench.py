@@ -94,54 +94,70 @@ def unmasked_pairs(mask, L):
 
 
 class ClockSampler:
-    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+    """nvidia-smi sampling of SM clock and throttle reasons.  The sampler process is started before the
+    warm-up (it needs ~0.2 s to come up); `begin()` / `end()` bracket the timed region and only samples
+    stamped inside it are used - if the region is shorter than the sampling period, the samples taken under
+    load since the warm-up started are used instead and the result says so."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device_index):
         self.idx = device_index
         self.proc = None
-
-    def __enter__(self):
+        self.t0 = self.t1 = None
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+
+    def begin(self):
+        self.t0 = time.time()
+
+    def end(self):
+        self.t1 = time.time()
+
+    def __enter__(self):
+        self.begin()
         return self
 
     def __exit__(self, *exc):
-        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.end()
         if self.proc is None:
             return
-        time.sleep(0.15)
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        clocks, reasons, maxc = [], set(), None
+        import datetime
+
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        rows = []
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                clocks.append(float(f[1]))
-                maxc = float(f[2])
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), [nm for nm, val in zip(names, f[5:9]) if val.lower().startswith("active")]))
             except ValueError:
                 continue
-            for nm, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(nm)
-        if clocks:
-            busy = [c for c in clocks if c > 0.5 * max(clocks)] or clocks
-            self.result = {"sm_mhz": statistics.median(busy), "sm_max_mhz": maxc, "reasons": sorted(reasons),
-                           "samples": len(clocks)}
+        inside = [r for r in rows if self.t0 - 0.02 <= r[0] <= self.t1 + 0.02]
+        window = "timed region"
+        if not inside:
+            mx = max((r[1] for r in rows), default=0.0)
+            inside = [r for r in rows if r[1] > 0.5 * mx]
+            window = "warm-up + timed region (timed region shorter than the 50 ms sampling period)"
+        if inside:
+            self.result = {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": inside[-1][2],
+                           "reasons": sorted({nm for r in inside for nm in r[3]}), "samples": len(inside), "window": window}
 
 
 def make_host_inputs(name, B, seed):
@@ -220,11 +236,12 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    clk = ClockSampler(local)
     for _ in range(args.warmup):
         step()
     barrier()
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
-    with ClockSampler(local) as clk:
+    with clk:
         barrier()
         t_host0 = time.perf_counter()
         for i in range(args.steps):

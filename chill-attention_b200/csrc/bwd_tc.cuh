@@ -319,6 +319,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const bool full = M::kHasQFullRange && qg0 >= full_lo && qg0 + kTile <= full_hi && qg0 + kTile <= n &&
                         qi * kTile + kTile <= g.Lq && kg0 + kTile <= n && kb + kTile <= g.Lk;
       const int qlim = imin(n - qg0, g.Lq - qi * kTile);
+      int w_lo = 0, w_hi = -1;  // visible query columns of this key row inside the tile (interval functors)
+      if (interval_rows<M>::value && !full && key_ok) row_window<M, false>(kg, qg0, qlim, n, g.margs, w_lo, w_hi);
 
       // ---- step 1: P^T = 2^(S^T c - LSE), masked; 16-bit copy to TMEM for the dV GEMM, kept packed in registers
       ok = mbar_wait(bar_s_full, par, guard, kStBwdCompute);
@@ -343,10 +345,17 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                           ((2 * j + 1) % CHILL_BWD_POLY_DEN) < CHILL_BWD_POLY_NUM), p2, p3);
             if (kMasked) {
               const int cq = c0 + 4 * j;
-              p0 = (key_ok && cq < qlim && M::mask(qg0 + cq, kg, n, g.margs)) ? p0 : 0.f;
-              p1 = (key_ok && cq + 1 < qlim && M::mask(qg0 + cq + 1, kg, n, g.margs)) ? p1 : 0.f;
-              p2 = (key_ok && cq + 2 < qlim && M::mask(qg0 + cq + 2, kg, n, g.margs)) ? p2 : 0.f;
-              p3 = (key_ok && cq + 3 < qlim && M::mask(qg0 + cq + 3, kg, n, g.margs)) ? p3 : 0.f;
+              if (interval_rows<M>::value) {
+                p0 = (cq >= w_lo && cq <= w_hi) ? p0 : 0.f;
+                p1 = (cq + 1 >= w_lo && cq + 1 <= w_hi) ? p1 : 0.f;
+                p2 = (cq + 2 >= w_lo && cq + 2 <= w_hi) ? p2 : 0.f;
+                p3 = (cq + 3 >= w_lo && cq + 3 <= w_hi) ? p3 : 0.f;
+              } else {
+                p0 = (key_ok && cq < qlim && M::mask(qg0 + cq, kg, n, g.margs)) ? p0 : 0.f;
+                p1 = (key_ok && cq + 1 < qlim && M::mask(qg0 + cq + 1, kg, n, g.margs)) ? p1 : 0.f;
+                p2 = (key_ok && cq + 2 < qlim && M::mask(qg0 + cq + 2, kg, n, g.margs)) ? p2 : 0.f;
+                p3 = (key_ok && cq + 3 < qlim && M::mask(qg0 + cq + 3, kg, n, g.margs)) ? p3 : 0.f;
+              }
             }
             preg[2 * j] = pack2<T>(p0, p1);
             preg[2 * j + 1] = pack2<T>(p2, p3);
@@ -639,6 +648,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         kt * kTile + kTile <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * kTile);
       const uint32_t tSb = tS + (it & 1) * 128;
+      int w_lo = 0, w_hi = -1;  // visible key columns of this query row inside the tile (interval functors)
+      if (interval_rows<M>::value && !full) row_window<M, true>(qg, kg0, klim, n, g.margs, w_lo, w_hi);
       // ---- step 1: P = 2^(S c - LSE) as soon as S(it) is there (it was issued a tile ahead); kept packed
       ok = mbar_wait(bar_s_full + 8 * (it & 1), (uint32_t)(it >> 1) & 1u, guard, kStDqCompute);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
@@ -660,8 +671,13 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  p0, p1);
             if (kMasked) {
               const int col = cbase + 2 * i;
-              p0 = (col < klim && M::mask(qg, kg0 + col, n, g.margs)) ? p0 : 0.f;
-              p1 = (col + 1 < klim && M::mask(qg, kg0 + col + 1, n, g.margs)) ? p1 : 0.f;
+              if (interval_rows<M>::value) {
+                p0 = (col >= w_lo && col <= w_hi) ? p0 : 0.f;
+                p1 = (col + 1 >= w_lo && col + 1 <= w_hi) ? p1 : 0.f;
+              } else {
+                p0 = (col < klim && M::mask(qg, kg0 + col, n, g.margs)) ? p0 : 0.f;
+                p1 = (col + 1 < klim && M::mask(qg, kg0 + col + 1, n, g.margs)) ? p1 : 0.f;
+              }
             }
             preg[hf][i] = pack2<T>(p0, p1);
           }

@@ -93,10 +93,17 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tS + lane_sel + q4 * 32, sreg + q4 * 32);
   tmem_wait_ld();
   if (!full) {
+    if (interval_rows<M>::value) {  // two per-row bounds instead of a mask() call per element
+      int c_lo, c_hi;
+      row_window<M, true>(qg, kg0, klim, n, margs, c_lo, c_hi);
 #pragma unroll
-    for (int cidx = 0; cidx < kTile; ++cidx) {
-      const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, margs);
-      sreg[cidx] = vis ? sreg[cidx] : 0xff800000u;  // -inf
+      for (int cidx = 0; cidx < kTile; ++cidx) sreg[cidx] = (cidx >= c_lo && cidx <= c_hi) ? sreg[cidx] : 0xff800000u;
+    } else {
+#pragma unroll
+      for (int cidx = 0; cidx < kTile; ++cidx) {
+        const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, margs);
+        sreg[cidx] = vis ? sreg[cidx] : 0xff800000u;  // -inf
+      }
     }
   }
   float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;

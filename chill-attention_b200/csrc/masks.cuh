@@ -15,10 +15,16 @@
 //   constexpr bool kHasKFullRange, kHasQFullRange     the two full-range functions are meaningful
 //   constexpr bool kKLimsContinuous, kQLimsContinuous a tile's range = [range(first).lo, range(last).hi]
 //   constexpr bool kGuaranteedSafe                    every query sees at least one key
+//   constexpr bool kIntervalRows (optional, default false)   mask(q, k) == (k_range_for_q(q).lo <= k <= .hi) and
+//                                                      == (q_range_for_k(k).lo <= q <= .hi): visible sets are intervals,
+//                                                      so boundary tiles compare column indices against two per-row
+//                                                      bounds instead of evaluating mask() per element
 //
 // The key-length bound (k < lens[b]) is applied by the kernels, not by the functor.
 #pragma once
 #include <stdint.h>
+
+#include <type_traits>
 
 #ifndef __CUDACC__
 #define __host__
@@ -39,6 +45,7 @@ CHILL_HD int imin(int a, int b) { return a < b ? a : b; }
 // chill_attention/mask.py:806-889
 struct FullMask {
   static constexpr bool kHasKFullRange = true, kHasQFullRange = true;
+  static constexpr bool kIntervalRows = true;
   static constexpr bool kKLimsContinuous = true, kQLimsContinuous = true, kGuaranteedSafe = true;
   CHILL_HD static bool mask(int, int, int, const MaskArgs&) { return true; }
   CHILL_HD static void k_range_for_q(int, int n, const MaskArgs&, int& lo, int& hi) { lo = 0; hi = n - 1; }
@@ -51,6 +58,7 @@ struct FullMask {
 // chill_attention/mask.py:892-976
 struct CausalMask {
   static constexpr bool kHasKFullRange = true, kHasQFullRange = true;
+  static constexpr bool kIntervalRows = true;
   static constexpr bool kKLimsContinuous = true, kQLimsContinuous = true, kGuaranteedSafe = true;
   CHILL_HD static bool mask(int q, int k, int, const MaskArgs&) { return q >= k; }
   CHILL_HD static void k_range_for_q(int q, int, const MaskArgs&, int& lo, int& hi) { lo = 0; hi = q; }
@@ -66,6 +74,7 @@ struct CausalMask {
 // chill_attention/mask.py:979-1108; args: left_context, right_context
 struct SlidingWindowMask {
   static constexpr bool kHasKFullRange = true, kHasQFullRange = true;
+  static constexpr bool kIntervalRows = true;
   static constexpr bool kKLimsContinuous = true, kQLimsContinuous = true, kGuaranteedSafe = false;
   CHILL_HD static bool mask(int q, int k, int, const MaskArgs& a) { return (k <= q + a.i[1]) && (k >= q - a.i[0]); }
   CHILL_HD static void k_range_for_q(int q, int n, const MaskArgs& a, int& lo, int& hi) {
@@ -97,6 +106,7 @@ struct SlidingWindowMask {
 // chill_attention/mask.py:1111-1266; args: context_size, back_contexts
 struct ChunkwiseMask {
   static constexpr bool kHasKFullRange = true, kHasQFullRange = true;
+  static constexpr bool kIntervalRows = true;
   static constexpr bool kKLimsContinuous = true, kQLimsContinuous = true, kGuaranteedSafe = false;
   CHILL_HD static bool mask(int q, int k, int, const MaskArgs& a) {
     const int d = q / a.i[0] - k / a.i[0];
@@ -132,6 +142,7 @@ struct ChunkwiseMask {
 // chill_attention/mask.py:1269-1394; args: prefix_size
 struct PrefixLMMask {
   static constexpr bool kHasKFullRange = true, kHasQFullRange = true;
+  static constexpr bool kIntervalRows = true;
   static constexpr bool kKLimsContinuous = true, kQLimsContinuous = true, kGuaranteedSafe = true;
   CHILL_HD static bool mask(int q, int k, int, const MaskArgs& a) { return k < a.i[0] || q >= k; }
   CHILL_HD static void k_range_for_q(int q, int n, const MaskArgs& a, int& lo, int& hi) {
@@ -161,6 +172,25 @@ struct PrefixLMMask {
     return (k + kt - 1 <= q) || (q + qt <= a.i[0] && k + kt <= a.i[0]);
   }
 };
+
+// kIntervalRows of a functor, false when it does not declare it.
+template <class M, class = void>
+struct interval_rows : std::false_type {};
+template <class M>
+struct interval_rows<M, std::void_t<decltype(M::kIntervalRows)>> : std::bool_constant<M::kIntervalRows> {};
+
+// Visible column window [c_lo, c_hi] (inclusive, tile-local, empty when c_hi < c_lo) of one row of a boundary
+// tile for interval functors.  KForQ: the row is query `pos`, columns are keys starting at global `col0`;
+// otherwise the row is key `pos`, columns are queries.  `ncols` = number of existing columns in the tile.
+template <class M, bool KForQ>
+CHILL_HD void row_window(int pos, int col0, int ncols, int n, const MaskArgs& a, int& c_lo, int& c_hi) {
+  int lo, hi;
+  if (KForQ) M::k_range_for_q(pos, n, a, lo, hi);
+  else M::q_range_for_k(pos, n, a, lo, hi);
+  c_lo = imax(lo - col0, 0);
+  c_hi = imin(imin(hi, n - 1) - col0, ncols - 1);
+  if (pos >= n || pos < 0) c_hi = -1;
+}
 
 // ----------------------------------------------------------------------------------------
 // Tile-loop clipping, shared by every kernel (reference: chill_attention/utils.py:221-272).

@@ -136,5 +136,9 @@ def test_device_functors_equal_host_functions(mask, _lib):
         lo, hi = fn(pos, n, mask.constargs)
         exp = torch.stack([torch.as_tensor(lo).expand(n), torch.as_tensor(hi).expand(n)], 1).int()
         assert torch.equal(table.cpu(), exp)
+    # the built-in functors declare kIntervalRows: every row and every column of the mask is exactly its range
+    d, kl, ql = dense.cpu().reshape(n, n).bool(), k_lims.cpu().long(), q_lims.cpu().long()
+    assert torch.equal(d, (pos[None, :] >= kl[:, :1]) & (pos[None, :] <= kl[:, 1:]))
+    assert torch.equal(d, (pos[:, None] >= ql[:, 0][None, :]) & (pos[:, None] <= ql[:, 1][None, :]))
     assert torch.equal(k_full.cpu(), mask._calc_full_ranges(n, tile, cls.k_full_range_for_q))
     assert torch.equal(q_full.cpu(), mask._calc_full_ranges(n, tile, cls.q_full_range_for_k))
