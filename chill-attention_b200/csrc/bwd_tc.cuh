@@ -165,22 +165,35 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
   const Guard guard{p.status, abort_flag};
 
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    mbar_init(bar_kv_full, 1);
-    mbar_init(bar_acc_full, 1);
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_dp_full, 1);
-    mbar_init(bar_p_full, kBwdComputeThreads / 32);
-    mbar_init(bar_ds_full, kBwdComputeThreads / 32);
-    for (int s = 0; s < L::kStages; ++s) {
-      mbar_init(bar_ring_full + 8 * s, 1);
-      mbar_init(bar_ring_empty + 8 * s, 1);
-    }
-    fence_barrier_init();
-    fence_proxy_async_smem();
-  }
   if (warp == 8) {
+    // The producer thread initialises the barriers itself and puts K, V and the first Q/dO tile in flight
+    // before the CTA-wide set-up (TMEM allocation, __syncthreads) completes.
+    if (lane == 0) {
+      *abort_flag = 0;
+      mbar_init(bar_kv_full, 1);
+      mbar_init(bar_acc_full, 1);
+      mbar_init(bar_s_full, 1);
+      mbar_init(bar_dp_full, 1);
+      mbar_init(bar_p_full, kBwdComputeThreads / 32);
+      mbar_init(bar_ds_full, kBwdComputeThreads / 32);
+      for (int s = 0; s < L::kStages; ++s) {
+        mbar_init(bar_ring_full + 8 * s, 1);
+        mbar_init(bar_ring_empty + 8 * s, 1);
+      }
+      fence_barrier_init();
+      fence_proxy_async_smem();
+      mbar_arrive_expect_tx(bar_kv_full, 2 * L::kTileBytes);
+      for (int c = 0; c < kChunks; ++c) {
+        tma_load_4d(sK + c * kChunkBytes, &tmK, bar_kv_full, c * 64, kb, hk, b);
+        tma_load_4d(sV + c * kChunkBytes, &tmV, bar_kv_full, c * 64, kb, hk, b);
+      }
+      mbar_arrive_expect_tx(bar_ring_full, 2 * L::kTileBytes);
+      for (int c = 0; c < kChunks; ++c) {
+        tma_load_4d(sRing + c * kChunkBytes, &tmQ, bar_ring_full, c * 64, qt_lo * kTile, hk * G, b);
+        tma_load_4d(sRing + L::kTileBytes + c * kChunkBytes, &tmdO, bar_ring_full, c * 64, qt_lo * kTile, hk * G, b);
+      }
+    }
+    __syncwarp();
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColsBwd);
     tmem_relinquish();
   }
@@ -193,15 +206,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 8) {
     // --------------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      prefetch_tmap(&tmQ);
-      prefetch_tmap(&tmdO);
-      mbar_arrive_expect_tx(bar_kv_full, 2 * L::kTileBytes);
-      for (int c = 0; c < kChunks; ++c) {
-        tma_load_4d(sK + c * kChunkBytes, &tmK, bar_kv_full, c * 64, kb, hk, b);
-        tma_load_4d(sV + c * kChunkBytes, &tmV, bar_kv_full, c * 64, kb, hk, b);
-      }
       bool ok = true;
-      for (int it = 0; it < n_it; ++it) {
+      for (int it = 1; it < n_it; ++it) {  // tile 0 was issued during set-up
         const int s = it % L::kStages;
         const uint32_t ph = (uint32_t)(it / L::kStages) & 1u;
         const int h = hk * G + it / n_qt;
@@ -508,27 +514,39 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
   const Guard guard{p.status, abort_flag};
 
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    mbar_init(bar_q_full, 1);
-    mbar_init(bar_acc_full, 1);
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_s_full + 8, 1);
-    mbar_init(bar_dp_full, 1);
-    mbar_init(bar_p_full, kBwdComputeThreads / 32);
-    mbar_init(bar_p_full + 8, kBwdComputeThreads / 32);
-    for (int s = 0; s < L::kKStages; ++s) {
-      mbar_init(bar_k_full + 8 * s, 1);
-      mbar_init(bar_k_empty + 8 * s, 1);
-    }
-    for (int s = 0; s < L::kVStages; ++s) {
-      mbar_init(bar_v_full + 8 * s, 1);
-      mbar_init(bar_v_empty + 8 * s, 1);
-    }
-    fence_barrier_init();
-    fence_proxy_async_smem();
-  }
   if (warp == 8) {
+    // The producer thread initialises the barriers itself and puts Q, dO and the first K/V tile in flight
+    // before the CTA-wide set-up (TMEM allocation, __syncthreads) completes.
+    if (lane == 0) {
+      *abort_flag = 0;
+      mbar_init(bar_q_full, 1);
+      mbar_init(bar_acc_full, 1);
+      mbar_init(bar_s_full, 1);
+      mbar_init(bar_s_full + 8, 1);
+      mbar_init(bar_dp_full, 1);
+      mbar_init(bar_p_full, kBwdComputeThreads / 32);
+      mbar_init(bar_p_full + 8, kBwdComputeThreads / 32);
+      for (int s = 0; s < L::kKStages; ++s) {
+        mbar_init(bar_k_full + 8 * s, 1);
+        mbar_init(bar_k_empty + 8 * s, 1);
+      }
+      for (int s = 0; s < L::kVStages; ++s) {
+        mbar_init(bar_v_full + 8 * s, 1);
+        mbar_init(bar_v_empty + 8 * s, 1);
+      }
+      fence_barrier_init();
+      fence_proxy_async_smem();
+      mbar_arrive_expect_tx(bar_q_full, 2 * L::kTileBytes);
+      for (int c = 0; c < kChunks; ++c) {
+        tma_load_4d(sQ + c * kChunkBytes, &tmQ, bar_q_full, c * 64, qb, h, b);
+        tma_load_4d(sdO + c * kChunkBytes, &tmdO, bar_q_full, c * 64, qb, h, b);
+      }
+      mbar_arrive_expect_tx(bar_k_full, L::kTileBytes);
+      for (int c = 0; c < kChunks; ++c) tma_load_4d(sKr + c * kChunkBytes, &tmK, bar_k_full, c * 64, kt_lo * kTile, hk, b);
+      mbar_arrive_expect_tx(bar_v_full, L::kTileBytes);
+      for (int c = 0; c < kChunks; ++c) tma_load_4d(sVr + c * kChunkBytes, &tmV, bar_v_full, c * 64, kt_lo * kTile, hk, b);
+    }
+    __syncwarp();
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColsBwd);
     tmem_relinquish();
   }
@@ -541,15 +559,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 8) {
     // --------------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      prefetch_tmap(&tmK);
-      prefetch_tmap(&tmV);
-      mbar_arrive_expect_tx(bar_q_full, 2 * L::kTileBytes);
-      for (int c = 0; c < kChunks; ++c) {
-        tma_load_4d(sQ + c * kChunkBytes, &tmQ, bar_q_full, c * 64, qb, h, b);
-        tma_load_4d(sdO + c * kChunkBytes, &tmdO, bar_q_full, c * 64, qb, h, b);
-      }
       bool ok = true;
-      for (int it = 0; it < n_it; ++it) {
+      for (int it = 1; it < n_it; ++it) {  // tile 0 was issued during set-up
         const int ks = it % L::kKStages, vs = it % L::kVStages;
         const int krow = (kt_lo + it) * kTile;
         ok = mbar_wait(bar_k_empty + 8 * ks, ((uint32_t)(it / L::kKStages) & 1u) ^ 1u, guard, kStDqProducer);

@@ -265,22 +265,33 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
   const Guard guard{p.status, abort_flag};
 
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    mbar_init(bar_q_full, 1);
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, 4);
-    mbar_init(bar_o_full, 1);
-    for (int s = 0; s < NSTAGE; ++s) {
-      mbar_init(bar_k_full + 8 * s, 1);
-      mbar_init(bar_k_empty + 8 * s, 1);
-      mbar_init(bar_v_full + 8 * s, 1);
-      mbar_init(bar_v_empty + 8 * s, 1);
-    }
-    fence_barrier_init();
-    fence_proxy_async_smem();
-  }
   if (warp == 4) {
+    // The producer thread initialises the barriers itself, so it can put Q and the first K/V tile in flight
+    // before the CTA-wide set-up (TMEM allocation, __syncthreads) completes instead of after it.
+    if (lane == 0) {
+      *abort_flag = 0;
+      mbar_init(bar_q_full, 1);
+      mbar_init(bar_s_full, 1);
+      mbar_init(bar_p_full, 4);
+      mbar_init(bar_o_full, 1);
+      for (int s = 0; s < NSTAGE; ++s) {
+        mbar_init(bar_k_full + 8 * s, 1);
+        mbar_init(bar_k_empty + 8 * s, 1);
+        mbar_init(bar_v_full + 8 * s, 1);
+        mbar_init(bar_v_empty + 8 * s, 1);
+      }
+      fence_barrier_init();
+      fence_proxy_async_smem();
+      if (n_tiles > 0) {
+        mbar_arrive_expect_tx(bar_q_full, L::kTileBytes);
+        for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * kChunkBytes, &tmQ, bar_q_full, c * 64, qb, h, b);
+        mbar_arrive_expect_tx(bar_k_full, L::kTileBytes);
+        for (int c = 0; c < kChunks; ++c) tma_load_4d(sK + c * kChunkBytes, &tmK, bar_k_full, c * 64, kt_lo * kTile, hk, b);
+        mbar_arrive_expect_tx(bar_v_full, L::kTileBytes);
+        for (int c = 0; c < kChunks; ++c) tma_load_4d(sV + c * kChunkBytes, &tmV, bar_v_full, c * 64, kt_lo * kTile, hk, b);
+      }
+    }
+    __syncwarp();
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColsFwd);
     tmem_relinquish();
   }
@@ -295,13 +306,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     reg_dealloc<kFwdOtherRegs>();
     // ------------------------------------------------------------------- TMA producer
     if (lane == 0 && n_tiles > 0) {
-      prefetch_tmap(&tmQ);
-      prefetch_tmap(&tmK);
-      prefetch_tmap(&tmV);
-      mbar_arrive_expect_tx(bar_q_full, L::kTileBytes);
-      for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * kChunkBytes, &tmQ, bar_q_full, c * 64, qb, h, b);
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      for (int j = 1; j < n_tiles && ok; ++j) {  // tile 0 was issued during set-up
         const int s = j % NSTAGE;
         const uint32_t ph = (uint32_t)(j / NSTAGE) & 1u;
         const int krow = (kt_lo + j) * kTile;
