@@ -293,19 +293,18 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int t = threadIdx.x;  // 0..255
     float* slot = rows_s + warp * 128;  // warp-private: [0,64) -LSE, [64,128) -delta of this warp's columns
     bool ok = true;
-    // -LSE / -delta of this lane's two query columns of tile `it`, fetched one tile ahead
-    auto fetch_rows = [&](int it, float* nl, float* nd) {
+    // LSE / delta of this lane's two query columns of tile `it`, fetched one tile ahead.  The loaded values are
+    // not touched until the next iteration (any dependent instruction here would stall on the global load).
+    auto fetch_rows = [&](int it, float* lv, float* dl) {
       const int h = hk * G + it / n_qt;
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int qrow = (qt_lo + it % n_qt) * kTile + c0 + e * 32 + lane;
-        nl[e] = 0.f;
-        nd[e] = 0.f;
-        if (qrow < g.Lq) {
-          const float lv = p.lse[b * p.lse_sb + h * p.lse_sh + qrow * p.lse_sl];
-          nl[e] = (lv == -CUDART_INF_F) ? 0.f : -lv;
-          nd[e] = -p.delta[((long long)b * g.H + h) * g.Lq + qrow];
-        }
+        const bool in = qrow < g.Lq;
+        const float* pl = p.lse + b * p.lse_sb + h * p.lse_sh + (in ? qrow : 0) * p.lse_sl;
+        const float* pd = p.delta + ((long long)b * g.H + h) * g.Lq + (in ? qrow : 0);
+        lv[e] = __ldg(pl);  // row 0 stands in for rows beyond Lq: those columns are masked out anyway
+        dl[e] = __ldg(pd);
       }
     };
     float nl_next[2], nd_next[2];
@@ -316,9 +315,9 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int qg0 = qi * kTile + g.q_off;
       __syncwarp();
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        slot[e * 32 + lane] = nl_next[e];
-        slot[64 + e * 32 + lane] = nd_next[e];
+      for (int e = 0; e < 2; ++e) {  // negated: they enter the packed FMA / ADD as addends
+        slot[e * 32 + lane] = (nl_next[e] == -CUDART_INF_F) ? 0.f : -nl_next[e];
+        slot[64 + e * 32 + lane] = -nd_next[e];
       }
       __syncwarp();
       if (it + 1 < n_it) fetch_rows(it + 1, nl_next, nd_next);
@@ -428,7 +427,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int cc = 0; cc < kChunks; ++cc)
         tma_store_4d(map, sRing + wg * L::kTileBytes + cc * kChunkBytes, cc * 64, kb, hk, b);
       tma_store_commit();
-      tma_store_wait_all();
+      tma_store_wait_read();  // shared memory may be released; the global writes complete by kernel end
     }
   }
 
@@ -742,7 +741,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (threadIdx.x == 0) {
       for (int cc = 0; cc < kChunks; ++cc) tma_store_4d(&tmdQ, sKr + cc * kChunkBytes, cc * 64, qb, h, b);
       tma_store_commit();
-      tma_store_wait_all();
+      tma_store_wait_read();  // shared memory may be released; the global writes complete by kernel end
     }
   }
 

@@ -281,7 +281,7 @@ fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int cc = 0; cc < kChunks; ++cc)
           tma_store_4d(&tmO, sQ + t * L::kTileBytes + cc * kChunkBytes, cc * 64, qb, h, b);
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();  // shared memory may be released; the global writes complete by kernel end
       }
     }
   }
