@@ -297,7 +297,33 @@ static int bwd_generic(const chill_bwd_args& a, cudaStream_t st) {
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "bwd_generic launch");
 }
 
-static int bwd_tc(const chill_bwd_args& a, cudaStream_t st) {
+// Side stream + fork/join events per device, created on first use: the dK/dV and the dQ kernel are
+// independent, so the second one starts filling SMs as the first one's last wave drains.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+
+static SideStream* side_stream() {
+  constexpr int kMaxDevices = 64;
+  static SideStream cache[kMaxDevices];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  SideStream& s = cache[dev];
+  if (s.stream == nullptr) {
+    if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+      s.stream = nullptr;
+      return nullptr;
+    }
+  }
+  return &s;
+}
+
+static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = true) {
   const chill_shape& s = a.s;
   CUtensorMap maps[7];
   const void* ptrs[7] = {a.q, a.k, a.v, a.d_o, a.dq, a.dk, a.dv};
@@ -321,6 +347,23 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st) {
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
   p.which = bwd_which(s.flags);
   int e = 0;
+  SideStream* side = (concurrent && p.which == 3) ? side_stream() : nullptr;
+  if (side != nullptr) {
+    // fork: dK/dV on the caller's stream, dQ on the side stream; join back before returning
+    cudaError_t ce = cudaEventRecord(side->fork, st);
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(side->stream, side->fork, 0);
+    if (ce != cudaSuccess) return cuda_fail(ce, "bwd fork");
+    p.which = 1;
+    CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd<MaskT>(s.dtype, s.D, maps, p, st)))
+    if (e == 0) {
+      p.which = 2;
+      CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd<MaskT>(s.dtype, s.D, maps, p, side->stream)))
+    }
+    ce = cudaEventRecord(side->join, side->stream);
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(st, side->join, 0);
+    if (ce != cudaSuccess) return cuda_fail(ce, "bwd join");
+    return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tc launch");
+  }
   CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd<MaskT>(s.dtype, s.D, maps, p, st)))
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tc launch");
 }
@@ -434,7 +477,7 @@ int chill_bwd_noalloc(const chill_bwd_args* a, void* stream) {
   b.delta = scratch;
   st = delta_launch(b, (cudaStream_t)stream);
   if (st != CHILL_OK) return st;
-  if (bwd_tc_eligible(b)) return bwd_tc(b, (cudaStream_t)stream);
+  if (bwd_tc_eligible(b)) return bwd_tc(b, (cudaStream_t)stream, /*concurrent=*/false);  // one stream, no helper objects
   if (b.s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
   return bwd_generic(b, (cudaStream_t)stream);
 }

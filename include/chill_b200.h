@@ -2,8 +2,12 @@
  * chill_b200.h - C ABI of the B200 (sm_100a) masked flash-attention kernels.
  *
  * Every entry point takes plain device pointers, element strides and sizes; none
- * allocates device memory, synchronises, or keeps state between calls (apart from
- * a per-process cache of the driver entry point used to encode TMA descriptors).
+ * allocates device memory, synchronises, or keeps state between calls, apart from a
+ * per-process cache of the driver entry point used to encode TMA descriptors and,
+ * for chill_bwd, one helper stream + two events per device (created on the first
+ * call) on which the dQ kernel runs beside the dK/dV kernel; chill_bwd joins that
+ * stream back into the caller's stream before it returns, so stream ordering as
+ * seen by the caller is unchanged.
  * All work is enqueued on the CUDA stream passed in (a cudaStream_t cast to
  * void*; NULL = the default stream) of the CURRENT device.  Return value: 0 on
  * success, a negative CHILL_E_* code otherwise; nothing aborts the process.
