@@ -215,31 +215,50 @@ def run_ours(args):
     bargs_dkdv = _cabi.backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape_dkdv)
     bargs_dq = _cabi.backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape_dq)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    kernels = ("fwd", "delta", "dkdv", "dq")
+    # --bwd fused: chill_bwd gets the fp32 dQ scratch and runs its single-kernel form (what chill_attention()
+    # does by default); --bwd split: the bitwise-reproducible two-kernel form (chill_attention.set_deterministic)
+    dq_accum = None
+    if args.bwd == "fused":
+        nacc = lib.chill_bwd_dq_accum_bytes(C.byref(shape))
+        if nacc:
+            dq_accum = torch.empty(nacc // 4, dtype=torch.float32, device=dev)
+    bargs_all = _cabi.backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape, dq_accum)
 
-    bargs_all = _cabi.backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape)
-
-    def step_plain():
-        # the path a caller runs: forward, delta, then chill_bwd (dK/dV and dQ kernels side by side)
+    def run_fwd():
         _cabi.forward(lib, q, k, v, o, lse, shape)
+
+    def run_delta():
         _cabi.check(lib, lib.chill_bwd_delta(C.byref(bargs_all), stream), "chill_bwd_delta")
+
+    def run_bwd():
         _cabi.check(lib, lib.chill_bwd(C.byref(bargs_all), stream), "chill_bwd")
 
-    def step(events=None):
-        if events is not None:
-            events[0].record()
-        _cabi.forward(lib, q, k, v, o, lse, shape)
-        if events is not None:
-            events[1].record()
-        _cabi.check(lib, lib.chill_bwd_delta(C.byref(bargs_dkdv), stream), "chill_bwd_delta")
-        if events is not None:
-            events[2].record()
+    def run_dkdv():
         _cabi.check(lib, lib.chill_bwd(C.byref(bargs_dkdv), stream), "chill_bwd(dkdv)")
-        if events is not None:
-            events[3].record()
+
+    def run_dq():
         _cabi.check(lib, lib.chill_bwd(C.byref(bargs_dq), stream), "chill_bwd(dq)")
-        if events is not None:
-            events[4].record()
+
+    if dq_accum is not None:
+        # "bwd" = zero-fill of the scratch + the fused kernel + the fp32 -> 16-bit conversion of dQ
+        parts = (("fwd", run_fwd), ("delta", run_delta), ("bwd", run_bwd))
+        kflops = {"fwd": 4.0, "bwd": 10.0}
+    else:
+        parts = (("fwd", run_fwd), ("delta", run_delta), ("dkdv", run_dkdv), ("dq", run_dq))
+        kflops = {"fwd": 4.0, "dkdv": 8.0, "dq": 6.0}
+    kernels = tuple(name for name, _ in parts)
+
+    def step_plain():
+        # the path a caller runs: forward, delta, then chill_bwd
+        run_fwd()
+        run_delta()
+        run_bwd()
+
+    def step(events):
+        for i, (_, fn) in enumerate(parts):
+            events[i].record()
+            fn()
+        events[len(parts)].record()
 
     def barrier():
         if world > 1:
@@ -262,7 +281,7 @@ def run_ours(args):
         t_host1 = time.perf_counter()
     total_ms = ev0.elapsed_time(ev1)
     # per-kernel durations: a second pass with the kernels launched one by one and an event between them
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(len(parts) + 1)] for _ in range(args.steps)]
     for i in range(args.steps):
         step(evs[i])
     barrier()
@@ -314,8 +333,7 @@ def run_ours(args):
         ms_per_step = total_ms / args.steps
         value = world * flops_step / (ms_per_step * 1e-3) / 1e12
         fwd_tflops = world * flops_fwd / (fwd_ms * 1e-3) / 1e12
-        kflops = {"fwd": 4.0, "dkdv": 8.0, "dq": 6.0}
-        dom = max(("fwd", "dkdv", "dq"), key=lambda kn: per_kernel[kn])
+        dom = max(kflops, key=lambda kn: per_kernel[kn])
         achieved = kflops[dom] * B * H * D * pairs / (per_kernel[dom] * 1e-3) / 1e12
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -326,7 +344,9 @@ def run_ours(args):
                        "parallelism": f"batch x head units sharded over {world} GPU(s), no collective",
                        "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no explicit flush"
                              % (8 * B * H * L * D * q.element_size() / 1e6),
-                       "tensor_core_path": bool(uses_tc == 1)},
+                       "tensor_core_path": bool(uses_tc == 1),
+                       "backward": "single kernel, 5 GEMMs per tile pair, dQ summed in fp32 scratch" if dq_accum is not None
+                                   else "two kernels (dK/dV, dQ), 7 GEMMs per tile pair, bitwise reproducible"},
             "fwd": {"tflops": round(fwd_tflops, 2), "ms": round(fwd_ms, 4),
                     "pct_of_measured_peak": round(100 * fwd_tflops / world / peak, 2),
                     "pct_of_nominal_peak": round(100 * fwd_tflops / world / NOMINAL_BF16_TFLOPS, 2)},
@@ -495,6 +515,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=("ours", "reference", "triton"))
     ap.add_argument("--triton-autotune", action="store_true", help="--impl triton: also time autotune=True")
+    ap.add_argument("--bwd", default="fused", choices=("fused", "split"), help="form of the backward pass")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work per baseline sample")

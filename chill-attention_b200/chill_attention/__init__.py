@@ -5,6 +5,7 @@ from .chill import (
     chill_attention,
     register_chill_mask,
 )
+from ._cabi import is_deterministic, set_deterministic
 from .mask import (
     CausalChillMask,
     ChillMask,
@@ -17,4 +18,5 @@ from .mask import (
 __all__ = [
     "chill_attention", "register_chill_mask", "_chill_reference_naive", "ChillMask", "FullChillMask",
     "CausalChillMask", "SlidingWindowChillMask", "ChunkwiseChillMask", "PrefixLMChillMask",
+    "set_deterministic", "is_deterministic",
 ]

@@ -32,8 +32,11 @@ BUILTIN_FUNCTOR_IDS = {
 
 _DTYPES = {torch.float32: CHILL_F32, torch.float16: CHILL_F16, torch.bfloat16: CHILL_BF16}
 
+ABI_VERSION = 2
+
 EXPORTS = (
-    "chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_bwd_scratch_bytes", "chill_fwd_uses_tensor_cores",
+    "chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_bwd_scratch_bytes", "chill_bwd_dq_accum_bytes",
+    "chill_fwd_uses_tensor_cores",
     "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits", "chill_read_device_status",
     "chill_abi_version", "chill_status_string", "chill_last_cuda_error",
 )
@@ -66,7 +69,7 @@ class BwdArgs(C.Structure):
                 ("d_o", C.c_void_p), ("lse", C.c_void_p), ("delta", C.c_void_p), ("dq", C.c_void_p),
                 ("dk", C.c_void_p), ("dv", C.c_void_p), ("q_strides", _S4), ("k_strides", _S4), ("v_strides", _S4),
                 ("o_strides", _S4), ("do_strides", _S4), ("dq_strides", _S4), ("dk_strides", _S4),
-                ("dv_strides", _S4), ("lse_strides", _S3)]
+                ("dv_strides", _S4), ("lse_strides", _S3), ("dq_accum", C.c_void_p)]
 
 
 class ChillLibraryError(RuntimeError):
@@ -96,6 +99,8 @@ def load_library(path: str | None = None) -> C.CDLL:
         lib.chill_bwd_noalloc.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
         lib.chill_bwd_scratch_bytes.argtypes = [C.POINTER(Shape)]
         lib.chill_bwd_scratch_bytes.restype = C.c_size_t
+        lib.chill_bwd_dq_accum_bytes.argtypes = [C.POINTER(Shape)]
+        lib.chill_bwd_dq_accum_bytes.restype = C.c_size_t
         lib.chill_fwd_uses_tensor_cores.argtypes = [C.POINTER(FwdArgs)]
         lib.chill_bwd_uses_tensor_cores.argtypes = [C.POINTER(BwdArgs)]
         lib.chill_mask_tabulate.argtypes = [C.POINTER(MaskDesc), C.c_int32, C.c_int32] + [C.c_void_p] * 6
@@ -107,8 +112,8 @@ def load_library(path: str | None = None) -> C.CDLL:
                      "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits",
                      "chill_read_device_status", "chill_abi_version"):
             getattr(lib, name).restype = C.c_int
-        if lib.chill_abi_version() != 1:
-            raise ChillLibraryError(f"{path}: ABI version {lib.chill_abi_version()} != 1")
+        if lib.chill_abi_version() != ABI_VERSION:
+            raise ChillLibraryError(f"{path}: ABI version {lib.chill_abi_version()} != {ABI_VERSION}")
         _libs[path] = lib
         return lib
 
@@ -166,7 +171,7 @@ def forward(lib, q, k, v, o, lse, shape: Shape):
     check(lib, lib.chill_fwd(C.byref(a), _stream()), "chill_fwd")
 
 
-def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape) -> BwdArgs:
+def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None) -> BwdArgs:
     a = BwdArgs()
     a.s = shape
     a.q, a.k, a.v, a.o, a.d_o = (t.data_ptr() for t in (q, k, v, o, do))
@@ -175,11 +180,41 @@ def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape) -> BwdAr
     (a.q_strides, a.k_strides, a.v_strides, a.o_strides, a.do_strides, a.dq_strides, a.dk_strides,
      a.dv_strides) = (_strides(t, 4) for t in (q, k, v, o, do, dq, dk, dv))
     a.lse_strides = _strides(lse, 3)
+    a.dq_accum = dq_accum.data_ptr() if dq_accum is not None else None
     return a
 
 
-def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape):
-    a = backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape)
+_deterministic = os.environ.get("CHILL_ATTENTION_DETERMINISTIC", "0") not in ("", "0")
+
+
+def set_deterministic(flag: bool) -> None:
+    """True: the backward never sums dQ with floating-point reductions (two-kernel backward, bitwise
+    reproducible); False (default): the single-kernel backward is used where it applies.  Also on when
+    ``torch.use_deterministic_algorithms(True)`` is set or CHILL_ATTENTION_DETERMINISTIC=1."""
+    global _deterministic
+    _deterministic = bool(flag)
+
+
+def is_deterministic() -> bool:
+    return _deterministic or torch.are_deterministic_algorithms_enabled()
+
+
+def dq_accum_for(lib, a: BwdArgs, device):
+    """The fp32 scratch tensor that switches chill_bwd to its single-kernel form, or None if the call
+    would not use it (generic kernels, deterministic mode)."""
+    if is_deterministic() or (a.s.flags & (FLAG_BWD_ONLY_DKDV | FLAG_BWD_ONLY_DQ)):
+        return None
+    nbytes = lib.chill_bwd_dq_accum_bytes(C.byref(a.s))
+    if nbytes == 0 or lib.chill_bwd_uses_tensor_cores(C.byref(a)) != 1:
+        return None
+    return torch.empty(nbytes // 4, dtype=torch.float32, device=device)
+
+
+def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None):
+    a = backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape, dq_accum)
+    if dq_accum is None:
+        dq_accum = dq_accum_for(lib, a, q.device)  # stays referenced until the launches are enqueued
+        a.dq_accum = dq_accum.data_ptr() if dq_accum is not None else None
     st = _stream()
     check(lib, lib.chill_bwd_delta(C.byref(a), st), "chill_bwd_delta")
     check(lib, lib.chill_bwd(C.byref(a), st), "chill_bwd")

@@ -18,13 +18,8 @@
 //
 // Roles in both (320 threads): warps 0-7 do the exponentials (thread (w % 4) * 32 + lane owns
 // TMEM lane = tile row; warps 0-3 and warps 4-7 split the columns), warp 8 is the TMA producer
-// and owns the TMEM allocation, warp 9 issues the MMAs.
-//
-// Software pipeline: the streamed tile is processed in two halves of 64 positions.  The score
-// accumulators (S/dP) are double-buffered in TMEM (2 x 64 columns each), and the MMA issuer runs
-// one half ahead: while the compute warps turn half u into P/dS, the tensor cores already work
-// on the scores of half u+1, and the accumulating GEMMs of half u follow as soon as its P/dS
-// are in TMEM.
+// and owns the TMEM allocation, warp 9 issues the MMAs.  Every MMA runs at full width (N = 128 or D):
+// tcgen05.mma at N = 64 takes as long as at N = 128 on this part.
 #pragma once
 #include <type_traits>
 
@@ -49,7 +44,15 @@ struct BwdTcParams {
   long long dq_sb, dq_sh, dq_sl, dk_sb, dk_sh, dk_sl, dv_sb, dv_sh, dv_sl;
   int* status;
   int which;  // bit0: launch the dK/dV kernel, bit1: launch the dQ kernel
+  float* dq_accum;  // fp32 accumulator of the single-kernel backward (bwd_fused.cuh), else nullptr
 };
+
+// fp32 dQ accumulator of the single-kernel backward (bwd_fused.cuh): one block of 128 rows x D channels per
+// (batch, head, query tile), stored as [4 row groups][D / 4][32 rows][4 channels]: the part a drain warp owns
+// (32 rows) is contiguous, and so is every run of channel groups inside it, so it leaves the SM as bulk reductions.
+__host__ __device__ inline size_t dq_accum_bytes(int B, int H, int Lq, int D) {
+  return (size_t)B * H * ((Lq + kTile - 1) / kTile) * kTile * D * sizeof(float);
+}
 
 template <int D>
 struct BwdSmem {

@@ -323,7 +323,7 @@ static SideStream* side_stream() {
   return &s;
 }
 
-static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = true) {
+static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = true, bool fused = true) {
   const chill_shape& s = a.s;
   CUtensorMap maps[7];
   const void* ptrs[7] = {a.q, a.k, a.v, a.d_o, a.dq, a.dk, a.dv};
@@ -346,7 +346,14 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = tr
   p.status = device_status_ptr();
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
   p.which = bwd_which(s.flags);
+  p.dq_accum = nullptr;
   int e = 0;
+  if (fused && p.which == 3 && a.dq_accum != nullptr) {
+    if ((reinterpret_cast<uintptr_t>(a.dq_accum) & 15u) != 0) return CHILL_E_INVALID;
+    p.dq_accum = a.dq_accum;  // single-kernel backward + conversion of the fp32 dQ sums
+    CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd<MaskT>(s.dtype, s.D, maps, p, st)))
+    return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_fused launch");
+  }
   SideStream* side = (concurrent && p.which == 3) ? side_stream() : nullptr;
   if (side != nullptr) {
     // fork: dK/dV on the caller's stream, dQ on the side stream; join back before returning
@@ -445,6 +452,12 @@ size_t chill_bwd_scratch_bytes(const chill_shape* s) {
   return (size_t)s->B * (size_t)s->H * (size_t)s->Lq * sizeof(float);
 }
 
+size_t chill_bwd_dq_accum_bytes(const chill_shape* s) {
+  if (s == nullptr || s->B <= 0 || s->H <= 0 || s->Lq <= 0) return 0;
+  if (s->dtype == CHILL_F32 || (s->D != 64 && s->D != 128)) return 0;
+  return tc::dq_accum_bytes(s->B, s->H, s->Lq, s->D);
+}
+
 int chill_bwd_delta(const chill_bwd_args* a, void* stream) {
   int st = check_bwd(a, false);
   if (st != CHILL_OK) return st;
@@ -477,7 +490,7 @@ int chill_bwd_noalloc(const chill_bwd_args* a, void* stream) {
   b.delta = scratch;
   st = delta_launch(b, (cudaStream_t)stream);
   if (st != CHILL_OK) return st;
-  if (bwd_tc_eligible(b)) return bwd_tc(b, (cudaStream_t)stream, /*concurrent=*/false);  // one stream, no helper objects
+  if (bwd_tc_eligible(b)) return bwd_tc(b, (cudaStream_t)stream, /*concurrent=*/false, /*fused=*/false);  // one stream, no helper objects
   if (b.s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
   return bwd_generic(b, (cudaStream_t)stream);
 }

@@ -1,5 +1,6 @@
 // Instantiates the tensor-core kernels for ONE mask functor: compile with
 //   -DCHILL_INST_MASK=<functor struct>   (e.g. CausalMask)
+#include "bwd_fused.cuh"
 #include "bwd_tc.cuh"
 #include "fwd_tc.cuh"
 #include "tc_launch.h"
@@ -89,6 +90,7 @@ int tc_launch_fwd<InstMask>(int dtype, int D, const CUtensorMap* maps, const tc:
 
 template <>
 int tc_launch_bwd<InstMask>(int dtype, int D, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st) {
+  if (p.dq_accum != nullptr) return tc::launch_bwd_fused_all<InstMask>(dtype, D, maps, p, st);
   return tc::launch_bwd_all<InstMask>(dtype, D, maps, p, st);
 }
 

@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define CHILL_ABI_VERSION 1
+#define CHILL_ABI_VERSION 2
 
 /* status codes */
 #define CHILL_OK 0
@@ -121,6 +121,14 @@ typedef struct chill_bwd_args {
   int64_t q_strides[4], k_strides[4], v_strides[4], o_strides[4], do_strides[4];
   int64_t dq_strides[4], dk_strides[4], dv_strides[4];
   int64_t lse_strides[3];
+  /* Optional (may be NULL): fp32 scratch of chill_bwd_dq_accum_bytes() bytes, 16-byte aligned, contents
+   * irrelevant on entry.  With it, and when the tensor-core kernels serve the call, chill_bwd runs its
+   * single-kernel backward: S and dP are computed once per tile pair (five GEMMs instead of seven) and the
+   * per-key-tile contributions to dQ are summed in this buffer with fp32 reductions, whose order is not
+   * fixed, so dQ may differ in its last bits from run to run (dK and dV do not).  Without it chill_bwd runs
+   * the deterministic two-kernel backward, which is also what the reference's accumulation order
+   * (chill_bwd_dq.py:300-394: one program owns a query tile) corresponds to. */
+  float* dq_accum;
 } chill_bwd_args;
 
 /* O = softmax(mask(Q K^T * sm_scale)) V and LSE.  See chill_shape for conventions. */
@@ -162,6 +170,10 @@ int chill_bwd_noalloc(const chill_bwd_args* a, void* stream);
 
 /* Bytes of the `delta` scratch buffer chill_bwd_delta / chill_bwd need. */
 size_t chill_bwd_scratch_bytes(const chill_shape* s);
+
+/* Bytes of the optional `dq_accum` scratch buffer (0 if the shape can never use it: fp32 data or a head
+ * dimension other than 64 / 128).  No counterpart in the reference. */
+size_t chill_bwd_dq_accum_bytes(const chill_shape* s);
 
 /* 1 if chill_fwd / chill_bwd would run the tcgen05 tensor-core kernels for these
  * arguments, 0 if the generic kernels, negative status if the arguments are invalid. */

@@ -39,11 +39,11 @@ def test_struct_sizes_match_header(lib):
     assert ctypes.sizeof(_cabi.MaskDesc) == 8 + 64 + 64
     assert ctypes.sizeof(_cabi.Shape) == 56 + 136
     assert ctypes.sizeof(_cabi.FwdArgs) == 192 + 5 * 8 + 4 * 32 + 24
-    assert ctypes.sizeof(_cabi.BwdArgs) == 192 + 10 * 8 + 8 * 32 + 24
+    assert ctypes.sizeof(_cabi.BwdArgs) == 192 + 10 * 8 + 8 * 32 + 24 + 8  # last: dq_accum
 
 
 def test_host_only_entry_points(lib):
-    assert lib.chill_abi_version() == 1
+    assert lib.chill_abi_version() == 2
     assert lib.chill_status_string(0) == b"ok"
     assert b"invalid" in lib.chill_status_string(-1)
     # bit0 k full range, bit1 q full range, bit2/3 continuous limits, bit4 guaranteed safe
@@ -70,6 +70,10 @@ def test_invalid_arguments_are_rejected_without_a_gpu(lib):
     s = _cabi.Shape()
     s.B, s.H, s.Lq = 2, 3, 5
     assert lib.chill_bwd_scratch_bytes(ctypes.byref(s)) == 2 * 3 * 5 * 4
+    s.D, s.dtype = 64, 2
+    assert lib.chill_bwd_dq_accum_bytes(ctypes.byref(s)) == 2 * 3 * 128 * 64 * 4  # whole query tiles
+    s.dtype = 0
+    assert lib.chill_bwd_dq_accum_bytes(ctypes.byref(s)) == 0  # fp32 data never takes that path
 
 
 def test_missing_library_fails_loudly(tmp_path):
