@@ -210,9 +210,11 @@ def dq_accum_for(lib, a: BwdArgs, device):
     return torch.empty(nbytes // 4, dtype=torch.float32, device=device)
 
 
-def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None):
+def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None, deterministic=False):
+    """chill_bwd_delta + chill_bwd.  Without `dq_accum` the fp32 dQ scratch of the single-kernel backward is
+    allocated here when the call can use it; `deterministic=True` forces the two-kernel form."""
     a = backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape, dq_accum)
-    if dq_accum is None:
+    if dq_accum is None and not deterministic:
         dq_accum = dq_accum_for(lib, a, q.device)  # stays referenced until the launches are enqueued
         a.dq_accum = dq_accum.data_ptr() if dq_accum is not None else None
     st = _stream()

@@ -3,10 +3,12 @@
 ``attention_fwd_bwd_host`` streams the batch through the GPU in chunks on three CUDA streams
 (host->device copies, kernels, device->host copies) with double-buffered device staging, so the
 PCIe transfers in both directions overlap each other and the kernels.  It drives the C ABI
-directly (forward, delta, dK/dV, dQ), no autograd graph.  Host tensors should be pinned
+directly (forward, delta, backward), no autograd graph.  Host tensors should be pinned
 (``tensor.pin_memory()``); pageable memory works but serialises the copies.
 """
 from __future__ import annotations
+
+import ctypes as C
 
 import torch
 
@@ -49,6 +51,12 @@ def attention_fwd_bwd_host(q, k, v, do, mask: ChillMask, sm_scale=None, out=None
                 "lse": dev((cb, H, L), torch.float32), "delta": dev((cb, H, L), torch.float32),
                 "in_free": None, "out_free": None,
             })
+        # fp32 dQ scratch of the single-kernel backward, one per slot like the other staging buffers (allocated
+        # here, on the caller's stream, so that the caching allocator can hand the same blocks out on the next call)
+        shape0 = _cabi.make_shape(slots[0]["in"][0], slots[0]["in"][1], functor, mask.constargs, None, sm_scale)
+        nacc = 0 if _cabi.is_deterministic() else lib.chill_bwd_dq_accum_bytes(C.byref(shape0))
+        for sl in slots:
+            sl["accum"] = dev((nacc // 4,), torch.float32) if nacc else None
         for i, b0 in enumerate(range(0, B, cb)):
             b1 = min(B, b0 + cb)
             n = b1 - b0
@@ -68,7 +76,11 @@ def attention_fwd_bwd_host(q, k, v, do, mask: ChillMask, sm_scale=None, out=None
                     s_cmp.wait_event(sl["out_free"])
                 shape = _cabi.make_shape(qd, kd, functor, mask.constargs, None, sm_scale)
                 _cabi.forward(lib, qd, kd, vd, od, sl["lse"][:n], shape)
-                _cabi.backward(lib, qd, kd, vd, od, dod, sl["lse"][:n], sl["delta"][:n], dqd, dkd, dvd, shape)
+                if sl["accum"] is not None:
+                    _cabi.backward(lib, qd, kd, vd, od, dod, sl["lse"][:n], sl["delta"][:n], dqd, dkd, dvd, shape, sl["accum"])
+                else:
+                    _cabi.backward(lib, qd, kd, vd, od, dod, sl["lse"][:n], sl["delta"][:n], dqd, dkd, dvd, shape,
+                                   deterministic=True)
                 ev_cmp = torch.cuda.Event()
                 ev_cmp.record(s_cmp)
                 sl["in_free"] = ev_cmp
