@@ -3,8 +3,9 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
 
-One "step" is one forward + backward pass (forward, delta, dK/dV, dQ kernels) over one
-synthetic batch of the workload.  The default workload is the configuration the headline
+One "step" is one forward + backward pass (chill_fwd, chill_bwd_delta, chill_bwd) over one
+synthetic batch of the workload; --bwd fused (default) gives chill_bwd the fp32 dQ scratch so that it runs
+its single-kernel form, --bwd split times the bitwise-reproducible two-kernel form.  The default workload is the configuration the headline
 metric is quoted on: CausalChillMask, bf16, (B, H, L, D) = (8, 16, 4096, 128), inputs ~N(0,1)
 seeded, sm_scale = D**-0.5.  Other workloads (c3, c4, c5 ...) are for kernel work, not for the
 reported line.
@@ -57,7 +58,9 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum per (batch, head) unit from the ncu capture summarised in
 # profiles/c2s_causal_bf16_kernels_ncu.md (causal bf16 L=4096 D=128, 32 units per launch); traffic grows in
 # proportion to the units a launch processes, so a full launch = per-unit figure x B x H.
-NCU_DRAM_BYTES_PER_UNIT = {("c2", "fwd"): 117.9e6 / 32, ("c2", "dkdv"): 176.5e6 / 32, ("c2", "dq"): 156.1e6 / 32}
+NCU_DRAM_BYTES_PER_UNIT = {("c2", "fwd"): 120.3e6 / 32, ("c2", "dkdv"): 176.5e6 / 32, ("c2", "dq"): 156.1e6 / 32,
+                           # single-kernel backward: bwd_fused_tc_kernel 290.2 MB + dq_convert_kernel 74.3 MB
+                           ("c2", "bwd"): (290.2e6 + 74.3e6) / 32}
 
 WORKLOADS = {
     # name: (mask class, mask args, dtype, B, H, L, D)
