@@ -31,20 +31,25 @@ constexpr int kTile = 128;          // query rows per CTA and keys per tile
 #ifndef CHILL_HEAD_GROUP
 #define CHILL_HEAD_GROUP 4
 #endif
-constexpr int kHeadGroup = CHILL_HEAD_GROUP;      // (batch, head) pairs scheduled together, see cta_order
+#ifndef CHILL_HEAD_GROUP_FWD
+#define CHILL_HEAD_GROUP_FWD 8
+#endif
+constexpr int kHeadGroup = CHILL_HEAD_GROUP;         // (batch, head) pairs scheduled together, see cta_order
+constexpr int kHeadGroupFwd = CHILL_HEAD_GROUP_FWD;  // the same for the forward kernel
 
-// CTA order of the 1-D grids: (batch, head) pairs are taken in groups of kHeadGroup; inside a group the
+// CTA order of the 1-D grids: (batch, head) pairs are taken in groups of `group`; inside a group the
 // tile rank is the slow index and the head the fast one.  With rank 0 = the longest tile (last query tile /
 // first key tile of a causal mask) the SMs drain from long to short work items, so the tail of a launch
-// consists of the shortest ones, while only kHeadGroup heads' K/V (or Q/dO) are live at a time, so the tiles
-// of one head still run close together and share their operands through L2.  Measured on one B200, fwd+bwd
-// TFLOP/s for group sizes 1 / 4 / 8 / 32: causal 739 / 755 / 750 / 731, full mask 795 / 812 / 800 / 744.
-__device__ __forceinline__ void cta_order(int idx, int n_hb, int n_tiles, int& hb, int& rank) {
-  const int per_group = kHeadGroup * n_tiles;
+// consists of the shortest ones, while only `group` heads' K/V (or Q/dO) are live at a time, so the tiles
+// of one head still run close together and share their operands through L2.  Measured on one B200 (causal bf16
+// B8 H16 L4096 D128), three alternating runs each: forward 0.577-0.587 ms with groups of 4, 0.562-0.567 ms with 8
+// or 16; single-kernel backward 1.456-1.466 ms with 4, 1.472-1.479 ms with 8 or 16; groups of 32 cost both 3-5 %.
+__device__ __forceinline__ void cta_order(int idx, int n_hb, int n_tiles, int& hb, int& rank, int group = kHeadGroup) {
+  const int per_group = group * n_tiles;
   const int grp = idx / per_group, rem = idx - grp * per_group;
-  const int heads_here = imin(kHeadGroup, n_hb - grp * kHeadGroup);
+  const int heads_here = imin(group, n_hb - grp * group);
   rank = rem / heads_here;
-  hb = grp * kHeadGroup + (rem - rank * heads_here);
+  hb = grp * group + (rem - rank * heads_here);
 }
 constexpr int kFwdThreads = 256;      // warps 0-3 softmax, 4 TMA producer, 5 MMA issuer, 6-7 idle
 constexpr int kFwdSoftmaxRegs = 200;  // per-thread register budget after setmaxnreg (2 CTAs/SM:
@@ -214,7 +219,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (g.Lq + kTile - 1) / kTile;
   int hb, rank;
-  cta_order((int)blockIdx.x, g.B * g.H, n_qt, hb, rank);
+  cta_order((int)blockIdx.x, g.B * g.H, n_qt, hb, rank, kHeadGroupFwd);
   const int qt = n_qt - 1 - rank;  // late (long) causal tiles first
   const int h = hb % g.H, b = hb / g.H;
   const int hk = h / (g.H / g.Hkv);

@@ -105,3 +105,65 @@ def test_deterministic_switch_gives_bitwise_repeatable_gradients(lib):
     for x, y in zip(loose, a):
         rel = ((x.double() - y.double()).norm() / y.double().norm()).item()
         assert rel <= G_RTOL[torch.bfloat16]
+
+
+@pytest.mark.parametrize("q0,k0", [(512, 256), (500, 300)])
+def test_shard_with_global_offsets_matches_the_full_problem(lib, q0, k0):
+    """Queries [q0, L) against keys [k0, L) of a sliding-window problem, with q_offset / k_offset / seq_len:
+    the rows a shard owns must equal the same rows of the unsharded result (what the sequence-sharded
+    multi-GPU path relies on), for both forms of the backward."""
+    import ctypes as C
+
+    import chill_attention as ca
+    from chill_attention import _cabi
+
+    L, D, W, dtype = 1024, 128, 200, torch.bfloat16
+    mask = ca.SlidingWindowChillMask(W, 0)
+    assert q0 - k0 >= W  # the key shard holds the whole window of its first query
+    q, k, v, do = make_inputs(1, 2, 2, L, D, dtype, seed=34)
+    o_ref, _, dq_ref, dk_ref, dv_ref = oracle_all(mask, q, k, v, do)
+    qs, dos = (t[:, :, q0:].contiguous().cuda() for t in (q, do))
+    ks, vs = (t[:, :, k0:].contiguous().cuda() for t in (k, v))
+    shape = _cabi.make_shape(qs, ks, _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor], mask.constargs, None, D ** -0.5,
+                             q_offset=q0, k_offset=k0, seq_len=L)
+    o = torch.empty_like(qs)
+    lse = torch.empty(1, 2, L - q0, dtype=torch.float32, device="cuda")
+    _cabi.forward(lib, qs, ks, vs, o, lse, shape)
+    assert (o.cpu().double() - o_ref[:, :, q0:]).abs().max().item() <= 2e-2
+    delta = torch.empty_like(lse)
+    accum = torch.empty(lib.chill_bwd_dq_accum_bytes(C.byref(shape)) // 4, dtype=torch.float32, device="cuda")
+    for scratch in (accum, None):
+        g = [torch.full_like(qs, float("nan")), torch.full_like(ks, float("nan")), torch.full_like(vs, float("nan"))]
+        a = _cabi.backward_args(qs, ks, vs, o, dos, lse, delta, *g, shape, scratch)
+        assert lib.chill_bwd_uses_tensor_cores(C.byref(a)) == 1
+        st = _cabi._stream()
+        _cabi.check(lib, lib.chill_bwd_delta(C.byref(a), st), "chill_bwd_delta")
+        _cabi.check(lib, lib.chill_bwd(C.byref(a), st), "chill_bwd")
+        torch.cuda.synchronize()
+        dq, dk, dv = (t.cpu().double() for t in g)
+        assert torch.isfinite(dq).all() and torch.isfinite(dk).all() and torch.isfinite(dv).all()
+        for name, got, ref in (("dq", dq, dq_ref[:, :, q0:]), ("dk", dk[:, :, q0 - k0:], dk_ref[:, :, q0:]),
+                               ("dv", dv[:, :, q0 - k0:], dv_ref[:, :, q0:])):
+            rel = ((got - ref).norm() / ref.norm()).item()
+            assert rel <= G_RTOL[dtype], f"{name}: {rel}"
+
+
+def test_misaligned_dq_scratch_is_rejected(lib):
+    import ctypes as C
+
+    import chill_attention as ca
+    from chill_attention import _cabi
+
+    mask = ca.CausalChillMask()
+    q, k, v, do = (t.cuda() for t in make_inputs(1, 1, 1, 256, 64, torch.float16, seed=35))
+    shape = _cabi.make_shape(q, k, _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor], mask.constargs, None, 0.125)
+    o, lse = torch.empty_like(q), torch.empty(1, 1, 256, dtype=torch.float32, device="cuda")
+    _cabi.forward(lib, q, k, v, o, lse, shape)
+    delta = torch.empty_like(lse)
+    accum = torch.empty(lib.chill_bwd_dq_accum_bytes(C.byref(shape)) // 4 + 4, dtype=torch.float32, device="cuda")
+    g = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    a = _cabi.backward_args(q, k, v, o, do, lse, delta, *g, shape, accum[1:])  # 4 bytes off a 16-byte boundary
+    st = _cabi._stream()
+    _cabi.check(lib, lib.chill_bwd_delta(C.byref(a), st), "chill_bwd_delta")
+    assert lib.chill_bwd(C.byref(a), st) == -1
+    torch.cuda.synchronize()
