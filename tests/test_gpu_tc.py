@@ -165,10 +165,20 @@ def test_host_buffer_pipeline_matches_device_path():
 
     mask = ca.CausalChillMask()
     q, k, v, do = make_inputs(5, 4, 2, 384, 128, torch.bfloat16)
-    o, lse, grads = run(mask, q, k, v, do)
     host = [t.pin_memory() for t in (q, k, v, do)]
-    for chunk in (1, 2, 8):
-        oh, dqh, dkh, dvh = attention_fwd_bwd_host(*host, mask, chunk_batches=chunk)
-        assert torch.equal(oh, o.detach().cpu())
-        for a, b in zip((dqh, dkh, dvh), grads):
-            assert torch.equal(a, b.cpu())
+    ca.set_deterministic(True)  # two-kernel backward: chunking must not change a single bit
+    try:
+        o, lse, grads = run(mask, q, k, v, do)
+        for chunk, heads in ((1, None), (2, 4), (8, 4), (1, 2)):
+            oh, dqh, dkh, dvh = attention_fwd_bwd_host(*host, mask, chunk_batches=chunk, chunk_heads=heads)
+            assert torch.equal(oh, o.detach().cpu())
+            for a, b in zip((dqh, dkh, dvh), grads):
+                assert torch.equal(a, b.cpu())
+    finally:
+        ca.set_deterministic(False)
+    # default (single-kernel backward, dQ summed with fp32 reductions): equal up to the order of those sums
+    oh, dqh, dkh, dvh = attention_fwd_bwd_host(*host, mask, chunk_heads=2)
+    assert torch.equal(oh, o.detach().cpu())
+    assert torch.equal(dkh, grads[1].cpu()) and torch.equal(dvh, grads[2].cpu())
+    rel = ((dqh.double() - grads[0].cpu().double()).norm() / grads[0].cpu().double().norm()).item()
+    assert rel <= 1e-2
