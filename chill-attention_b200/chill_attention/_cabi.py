@@ -32,7 +32,7 @@ BUILTIN_FUNCTOR_IDS = {
 
 _DTYPES = {torch.float32: CHILL_F32, torch.float16: CHILL_F16, torch.bfloat16: CHILL_BF16}
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 EXPORTS = (
     "chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_bwd_scratch_bytes", "chill_bwd_dq_accum_bytes",
@@ -69,7 +69,8 @@ class BwdArgs(C.Structure):
                 ("d_o", C.c_void_p), ("lse", C.c_void_p), ("delta", C.c_void_p), ("dq", C.c_void_p),
                 ("dk", C.c_void_p), ("dv", C.c_void_p), ("q_strides", _S4), ("k_strides", _S4), ("v_strides", _S4),
                 ("o_strides", _S4), ("do_strides", _S4), ("dq_strides", _S4), ("dk_strides", _S4),
-                ("dv_strides", _S4), ("lse_strides", _S3), ("dq_accum", C.c_void_p)]
+                ("dv_strides", _S4), ("lse_strides", _S3), ("dq_accum", C.c_void_p), ("d_lse", C.c_void_p),
+                ("dlse_strides", _S3)]
 
 
 class ChillLibraryError(RuntimeError):
@@ -171,7 +172,7 @@ def forward(lib, q, k, v, o, lse, shape: Shape):
     check(lib, lib.chill_fwd(C.byref(a), _stream()), "chill_fwd")
 
 
-def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None) -> BwdArgs:
+def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None, d_lse=None) -> BwdArgs:
     a = BwdArgs()
     a.s = shape
     a.q, a.k, a.v, a.o, a.d_o = (t.data_ptr() for t in (q, k, v, o, do))
@@ -181,6 +182,9 @@ def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum
      a.dv_strides) = (_strides(t, 4) for t in (q, k, v, o, do, dq, dk, dv))
     a.lse_strides = _strides(lse, 3)
     a.dq_accum = dq_accum.data_ptr() if dq_accum is not None else None
+    if d_lse is not None:  # gradient of the loss w.r.t. the returned LSE (log2 units), fp32 [B, H, L]
+        a.d_lse = d_lse.data_ptr()
+        a.dlse_strides = _strides(d_lse, 3)
     return a
 
 
@@ -210,10 +214,11 @@ def dq_accum_for(lib, a: BwdArgs, device):
     return torch.empty(nbytes // 4, dtype=torch.float32, device=device)
 
 
-def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None, deterministic=False):
+def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None, deterministic=False,
+             d_lse=None):
     """chill_bwd_delta + chill_bwd.  Without `dq_accum` the fp32 dQ scratch of the single-kernel backward is
     allocated here when the call can use it; `deterministic=True` forces the two-kernel form."""
-    a = backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape, dq_accum)
+    a = backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape, dq_accum, d_lse)
     if dq_accum is None and not deterministic:
         dq_accum = dq_accum_for(lib, a, q.device)  # stays referenced until the launches are enqueued
         a.dq_accum = dq_accum.data_ptr() if dq_accum is not None else None

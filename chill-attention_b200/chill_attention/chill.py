@@ -138,10 +138,46 @@ def register_chill_mask(mask: ChillMask):
             torch.empty_like(v, memory_format=torch.contiguous_format),
         )
 
+    # Same computation with one more input, the gradient that reached the returned LSE.  The reference has no
+    # such op: its backward drops that gradient (chill.py:466-490), so differentiating through `return_lse=True`
+    # silently gives wrong gradients there.  backward<Name> above keeps the reference's schema; this op is used
+    # only when a gradient for the LSE actually arrives.
+    @torch.library.custom_op(f"chill_attention::backward_with_dlse{mask_name}", mutates_args=(), device_types=("cuda",))
+    def attention_backward_dlse_adapter(
+        q: torch.Tensor,
+        k: torch.Tensor,
+        v: torch.Tensor,
+        lens: typing.Optional[torch.Tensor],
+        o: torch.Tensor,
+        lse: torch.Tensor,
+        do: torch.Tensor,
+        dlse: torch.Tensor,
+        mask_args: typing.List[typing.Union[int, float, bool]],
+        sm_scale: float,
+    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        with torch.cuda.device(q.device):
+            delta = torch.empty(o.shape[:-1], dtype=torch.float32, device=o.device)
+            DQ = torch.empty_like(q, memory_format=torch.contiguous_format)
+            DK = torch.empty_like(k, memory_format=torch.contiguous_format)
+            DV = torch.empty_like(v, memory_format=torch.contiguous_format)
+            lens_c = lens.contiguous() if lens is not None else None
+            shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale)
+            _cabi.backward(lib, q, k, v, o, do.contiguous(), lse, delta, DQ, DK, DV, shape, d_lse=dlse.float())
+        return DQ, DK, DV
+
+    @torch.library.register_fake(f"chill_attention::backward_with_dlse{mask_name}")
+    def attention_backward_dlse_adapter_abstract(q, k, v, lens, o, lse, do, dlse, mask_args, sm_scale):
+        return (
+            torch.empty_like(q, memory_format=torch.contiguous_format),
+            torch.empty_like(k, memory_format=torch.contiguous_format),
+            torch.empty_like(v, memory_format=torch.contiguous_format),
+        )
+
     def setup_context(ctx, inputs, output):
         O, LSE = output
         q, k, v, lens, mask_args, sm_scale, return_lse, prescale_qk, precision, autotune = inputs
         ctx.save_for_backward(q, k, v, O, LSE, lens)
+        ctx.set_materialize_grads(False)  # an unused output arrives as None instead of a tensor of zeros
         ctx.mask_args = mask_args
         ctx.sm_scale = sm_scale
         ctx.prescale_qk = prescale_qk
@@ -149,12 +185,19 @@ def register_chill_mask(mask: ChillMask):
         ctx.autotune = autotune
 
     def backward(ctx, do, dlse):
-        # like the reference, no gradient flows through a returned LSE (chill.py:466-490)
         q, k, v, o, lse, lens = ctx.saved_tensors
-        DQ, DK, DV = attention_backward_adapter(
-            q=q, k=k, v=v, lens=lens, o=o, lse=lse, do=do, mask_args=ctx.mask_args, sm_scale=ctx.sm_scale,
-            prescale_qk=ctx.prescale_qk, precision=ctx.precision, autotune=ctx.autotune,
-        )
+        if do is None:
+            do = torch.zeros_like(o)
+        if dlse is not None and dlse.numel() == lse.numel() and lse.numel() > 0:
+            # a gradient reached the returned LSE: propagate it (the reference drops it, chill.py:466-490)
+            DQ, DK, DV = attention_backward_dlse_adapter(
+                q=q, k=k, v=v, lens=lens, o=o, lse=lse, do=do, dlse=dlse, mask_args=ctx.mask_args, sm_scale=ctx.sm_scale,
+            )
+        else:
+            DQ, DK, DV = attention_backward_adapter(
+                q=q, k=k, v=v, lens=lens, o=o, lse=lse, do=do, mask_args=ctx.mask_args, sm_scale=ctx.sm_scale,
+                prescale_qk=ctx.prescale_qk, precision=ctx.precision, autotune=ctx.autotune,
+            )
         return DQ, DK, DV, None, None, None, None, None, None, None
 
     attention_forward_adapter.register_autograd(backward, setup_context=setup_context)

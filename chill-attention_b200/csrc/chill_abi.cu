@@ -253,6 +253,7 @@ static BwdP to_bwdp(const chill_bwd_args& a) {
 static int delta_launch(const chill_bwd_args& a, cudaStream_t st) {
   const chill_shape& s = a.s;
   const size_t es = esize(s.dtype);
+  const long long dl[3] = {a.d_lse ? a.dlse_strides[0] : 0, a.d_lse ? a.dlse_strides[1] : 0, a.d_lse ? a.dlse_strides[2] : 0};
   const bool fast = (s.dtype != CHILL_F32) && (s.D == 64 || s.D == 128) &&
                     tma_ok(a.o, a.o_strides, s.B, s.H, s.Lq, es) && tma_ok(a.d_o, a.do_strides, s.B, s.H, s.Lq, es);
   if (fast) {
@@ -261,7 +262,7 @@ static int delta_launch(const chill_bwd_args& a, cudaStream_t st) {
 #define CHILL_DELTA16(T, DD)                                                                                     \
   delta_rows16_kernel<T, DD><<<grid, 256, 0, st>>>((const T*)a.o, (const T*)a.d_o, a.delta, a.o_strides[0],        \
                                                    a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], \
-                                                   a.do_strides[2], s.H, s.Lq)
+                                                   a.do_strides[2], s.H, s.Lq, a.d_lse, dl[0], dl[1], dl[2])
     if (s.dtype == CHILL_BF16) {
       if (s.D == 64) CHILL_DELTA16(__nv_bfloat16, 64); else CHILL_DELTA16(__nv_bfloat16, 128);
     } else {
@@ -271,7 +272,7 @@ static int delta_launch(const chill_bwd_args& a, cudaStream_t st) {
   } else {
     dim3 grid((s.Lq + kGenericWarps - 1) / kGenericWarps, s.H, s.B);
     TRef o = to_ref(a.o, a.o_strides), d_o = to_ref(a.d_o, a.do_strides);
-    CHILL_DTYPE_SWITCH(s.dtype, (delta_kernel<ElemT><<<grid, kGenericWarps * 32, 0, st>>>(o, d_o, a.delta, s.H, s.Lq, s.D)))
+    CHILL_DTYPE_SWITCH(s.dtype, (delta_kernel<ElemT><<<grid, kGenericWarps * 32, 0, st>>>(o, d_o, a.delta, s.H, s.Lq, s.D, a.d_lse, dl[0], dl[1], dl[2])))
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "delta launch");

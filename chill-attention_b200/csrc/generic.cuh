@@ -168,7 +168,8 @@ __global__ void __launch_bounds__(kGenericWarps * 32) fwd_generic_kernel(FwdP p)
 // --------------------------------------------------------------------------------- delta
 // delta[b,h,t] = sum_d O*dO in fp32; one warp per row, every row (no `lens`), like the reference.
 template <typename T>
-__global__ void __launch_bounds__(kGenericWarps * 32) delta_kernel(TRef o, TRef d_o, float* delta, int H, int Lq, int D) {
+__global__ void __launch_bounds__(kGenericWarps * 32) delta_kernel(TRef o, TRef d_o, float* delta, int H, int Lq, int D,
+                                                                   const float* dlse, long long dl_sb, long long dl_sh, long long dl_sl) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kGenericWarps + warp;
   const int h = blockIdx.y, b = blockIdx.z;
@@ -178,6 +179,7 @@ __global__ void __launch_bounds__(kGenericWarps * 32) delta_kernel(TRef o, TRef 
   float acc = 0.f;
   for (int d = lane; d < D; d += 32) acc = fmaf(to_f(orow[d * o.sd]), to_f(drow[d * d_o.sd]), acc);
   acc = warp_sum(acc);
+  if (dlse != nullptr) acc -= kLog2e * dlse[b * dl_sb + h * dl_sh + row * dl_sl];  // gradient through the returned LSE
   if (lane == 0) delta[((long long)b * H + h) * Lq + row] = acc;
 }
 
@@ -187,7 +189,8 @@ template <typename T, int D>
 __global__ void __launch_bounds__(256) delta_rows16_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
                                                            float* __restrict__ delta, long long o_sb, long long o_sh,
                                                            long long o_sl, long long do_sb, long long do_sh,
-                                                           long long do_sl, int H, int Lq) {
+                                                           long long do_sl, int H, int Lq, const float* __restrict__ dlse,
+                                                           long long dl_sb, long long dl_sh, long long dl_sl) {
   constexpr int LPR = D / 8;  // lanes per row
   constexpr int RPW = 32 / LPR;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -205,7 +208,10 @@ __global__ void __launch_bounds__(256) delta_rows16_kernel(const T* __restrict__
   }
 #pragma unroll
   for (int ofs = LPR / 2; ofs > 0; ofs >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, ofs);
-  if (row < Lq && li == 0) delta[((long long)b * H + h) * Lq + row] = acc;
+  if (row < Lq && li == 0) {
+    if (dlse != nullptr) acc -= kLog2e * dlse[b * dl_sb + h * dl_sh + row * dl_sl];  // gradient through the returned LSE
+    delta[((long long)b * H + h) * Lq + row] = acc;
+  }
 }
 
 // ------------------------------------------------------------------------------ backward

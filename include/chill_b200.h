@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define CHILL_ABI_VERSION 2
+#define CHILL_ABI_VERSION 3
 
 /* status codes */
 #define CHILL_OK 0
@@ -129,12 +129,19 @@ typedef struct chill_bwd_args {
    * the deterministic two-kernel backward, which is also what the reference's accumulation order
    * (chill_bwd_dq.py:300-394: one program owns a query tile) corresponds to. */
   float* dq_accum;
+  /* Optional (may be NULL): gradient of the loss with respect to the LSE that chill_fwd returned (log2 units,
+   * same layout rules as lse).  chill_bwd_delta folds it into delta (delta -= log2(e) * d_lse), which is all the
+   * backward kernels need to propagate it to dQ and dK.  The reference drops this gradient (chill.py:466-490);
+   * with NULL the behaviour is the reference's. */
+  const float* d_lse;
+  int64_t dlse_strides[3];
 } chill_bwd_args;
 
 /* O = softmax(mask(Q K^T * sm_scale)) V and LSE.  See chill_shape for conventions. */
 int chill_fwd(const chill_fwd_args* a, void* stream);
 
-/* delta[b,h,t] = sum_d float(O[b,h,t,d]) * float(dO[b,h,t,d]).  Uses a->o, a->d_o, a->delta. */
+/* delta[b,h,t] = sum_d float(O[b,h,t,d]) * float(dO[b,h,t,d]) (- log2(e) * d_lse[b,h,t] if a->d_lse is given).
+ * Uses a->o, a->d_o, a->delta, a->d_lse. */
 int chill_bwd_delta(const chill_bwd_args* a, void* stream);
 
 /* dQ, dK, dV.  a->delta must hold the result of chill_bwd_delta for the same a->o / a->d_o

@@ -182,3 +182,37 @@ def test_host_buffer_pipeline_matches_device_path():
     assert torch.equal(dkh, grads[1].cpu()) and torch.equal(dvh, grads[2].cpu())
     rel = ((dqh.double() - grads[0].cpu().double()).norm() / grads[0].cpu().double().norm()).item()
     assert rel <= 1e-2
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64), (torch.float32, 32)], ids=str)
+def test_gradient_through_the_returned_lse(dtype, D):
+    """loss = <O, dO> + <LSE, dLSE>: the second term's gradient reaches dQ and dK (the reference drops it,
+    chill.py:466-490).  Expected values: autograd through a dense fp64 restatement."""
+    import math
+
+    import chill_attention as ca
+    from helpers import G_RTOL
+
+    B, H, Hkv, L = 2, 4, 2, 300
+    for mask in (ca.CausalChillMask(), ca.SlidingWindowChillMask(40, 10)):
+        q, k, v, do = make_inputs(B, H, Hkv, L, D, dtype, seed=41)
+        dlse = torch.randn(B, H, L, generator=torch.Generator().manual_seed(42))
+        qr, kr, vr = (t.double().requires_grad_(True) for t in (q, k, v))
+        ke, ve = (t.repeat_interleave(H // Hkv, dim=1) for t in (kr, vr))
+        s = (qr @ ke.transpose(-1, -2)) * D ** -0.5
+        s = s.masked_fill(~mask.make_mask(L, device="cpu"), float("-inf"))
+        lse2 = torch.logsumexp(s, dim=-1) * math.log2(math.e)
+        o_ref = torch.softmax(s, dim=-1) @ ve
+        ((o_ref * do.double()).sum() + (lse2 * dlse.double()).sum()).backward()
+        qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        o, lse = ca.chill_attention(qd, kd, vd, mask=mask, return_lse=True)
+        assert (lse.cpu().double() - lse2.detach()).abs().max().item() <= 2e-2
+        ((o.float() * do.cuda().float()).sum() + (lse * dlse.cuda()).sum()).backward()
+        for name, got, ref in (("dq", qd.grad, qr.grad), ("dk", kd.grad, kr.grad), ("dv", vd.grad, vr.grad)):
+            rel = ((got.cpu().double() - ref).norm() / ref.norm()).item()
+            assert rel <= 2 * G_RTOL[dtype], f"{mask} {name}: {rel}"
+        # only the LSE is used: dO arrives as None
+        qd2, kd2, vd2 = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        _, lse_only = ca.chill_attention(qd2, kd2, vd2, mask=mask, return_lse=True)
+        (lse_only * dlse.cuda()).sum().backward()
+        assert torch.isfinite(qd2.grad).all() and vd2.grad.abs().max().item() == 0.0
