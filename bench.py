@@ -510,6 +510,53 @@ def run_triton_reference(args):
                       "and zero-filled by the reference inside the timed region" % __import__("triton").__version__}), flush=True)
 
 
+def run_reference_shapes(args):
+    """The shapes of the reference's own benchmark (benchmark/benchmark.py:25-35, 38-55, 73): five masks x
+    {B8 H12 D64, B8 H4 D128} x T in linspace(128, 6000, 4), fp16, inputs N(0, 0.01); forward and backward
+    milliseconds through the public op, one JSON line per case.  An aid for like-for-like comparison with the
+    reference's published curves, not the reported metric."""
+    sys.path.insert(0, os.path.join(ROOT, "chill-attention_b200"))
+    import chill_attention as ca
+
+    torch.cuda.set_device(0)
+    masks = [ca.SlidingWindowChillMask(16, 16), ca.CausalChillMask(), ca.ChunkwiseChillMask(16, 8),
+             ca.PrefixLMChillMask(128), ca.FullChillMask()]
+    times = sorted({int(t) for t in torch.linspace(128, 6000, 4).tolist()})
+    for mask in masks:
+        for name, heads, dim in (("small", 12, 64), ("medium", 4, 128)):
+            for T in times:
+                g = torch.Generator(device="cuda").manual_seed(20)
+                q, k, v = (torch.empty(8, heads, T, dim, device="cuda", dtype=torch.float16).normal_(0.0, 0.01, generator=g)
+                           .requires_grad_() for _ in range(3))
+                do = torch.randn(8, heads, T, dim, device="cuda", dtype=torch.float16, generator=g)
+
+                def fwd():
+                    return ca.chill_attention(q, k, v, mask=mask)
+
+                o = fwd()
+
+                def bwd():
+                    o.backward(do, retain_graph=True)
+
+                res = {}
+                for what, fn in (("fwd", fwd), ("bwd", bwd)):
+                    for _ in range(max(3, args.warmup)):
+                        fn()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(args.steps):
+                        fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    res[what] = e0.elapsed_time(e1) / args.steps
+                pairs = unmasked_pairs(mask, T)
+                print(json.dumps({"mask": str(mask), "shape": name, "batch": 8, "heads": heads, "dim": dim, "time": T,
+                                  "dtype": "f16", "fwd_ms": round(res["fwd"], 4), "bwd_ms": round(res["bwd"], 4),
+                                  "fwd_tflops": round(4.0 * 8 * heads * dim * pairs / res["fwd"] / 1e9, 1),
+                                  "bwd_tflops": round(10.0 * 8 * heads * dim * pairs / res["bwd"] / 1e9, 1)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -519,12 +566,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference", "triton"))
     ap.add_argument("--triton-autotune", action="store_true", help="--impl triton: also time autotune=True")
     ap.add_argument("--bwd", default="fused", choices=("fused", "split"), help="form of the backward pass")
+    ap.add_argument("--reference-shapes", action="store_true",
+                    help="time the shapes of the reference's own benchmark script instead of a workload")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work per baseline sample")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "triton":
+    if args.reference_shapes:
+        run_reference_shapes(args)
+    elif args.impl == "triton":
         run_triton_reference(args)
     elif args.impl == "reference":
         run_reference(args)
