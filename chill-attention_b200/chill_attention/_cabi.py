@@ -19,7 +19,7 @@ DEFAULT_LIB = os.path.join(LIB_DIR, "libchill_b200.so")
 
 CHILL_F32, CHILL_F16, CHILL_BF16 = 0, 1, 2
 MASK_FULL, MASK_CAUSAL, MASK_SLIDING, MASK_CHUNKWISE, MASK_PREFIXLM, MASK_CUSTOM = range(6)
-FLAG_FORCE_GENERIC, FLAG_REQUIRE_TC, FLAG_BWD_ONLY_DKDV, FLAG_BWD_ONLY_DQ = 1, 2, 4, 8
+FLAG_FORCE_GENERIC, FLAG_REQUIRE_TC, FLAG_BWD_ONLY_DKDV, FLAG_BWD_ONLY_DQ, FLAG_ALLOW_TF32 = 1, 2, 4, 8, 16
 MAX_MASK_ARGS = 8
 
 BUILTIN_FUNCTOR_IDS = {

@@ -14,7 +14,8 @@ bodies hand raw device pointers to the C ABI (include/chill_b200.h); kernels run
 the current CUDA stream.  ``autotune`` and ``prescale_qk`` are accepted for
 compatibility and have no effect: there is nothing to tune at run time and the
 softmax scale is always applied in fp32 inside the exponent.
-``precision`` only matters for fp32 inputs, which are computed with IEEE fp32 FMAs.
+``precision`` only matters for fp32 inputs: "ieee" (default) computes them with IEEE fp32 FMAs, "tf32" lets the
+forward (head dim 64 / 128) run on the tensor cores in TF32; the backward of fp32 inputs is IEEE fp32 either way.
 """
 from __future__ import annotations
 
@@ -90,7 +91,9 @@ def register_chill_mask(mask: ChillMask):
             O = torch.empty_like(q, memory_format=torch.contiguous_format)
             LSE = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if return_lse else None
             lens_c = lens.contiguous() if lens is not None else None
-            shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale)
+            # precision="tf32" (the reference's tl.dot input_precision): fp32 tensors may use the TF32 tensor cores
+            flags = _cabi.FLAG_ALLOW_TF32 if (precision == "tf32" and q.dtype == torch.float32) else 0
+            shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale, flags=flags)
             _cabi.forward(lib, q, k, v, O, LSE, shape)
         if LSE is None:
             LSE = torch.empty(0, dtype=torch.float32, device=q.device)
@@ -260,7 +263,8 @@ def chill_attention(
         sm_scale: softmax scale, default head_dim ** -0.5.
         return_lse: also return the log-sum-exp of every row in log2 units, shape [batch, heads, seq_len].
         prescale_qk, autotune: accepted for compatibility with the reference, no effect.
-        precision: "ieee" or "tf32"; fp32 inputs are always computed with IEEE fp32 arithmetic.
+        precision: "ieee" or "tf32"; for fp32 inputs "tf32" runs the forward on the tensor cores in TF32
+            (head dim 64 / 128, ~1e-3 output error instead of ~1e-6), everything else is IEEE fp32.
 
     Returns: O, or (O, LSE) when ``return_lse``.
     """

@@ -115,22 +115,24 @@ static EncodeTiledFn encode_fn() {
 
 // Box = 64 channels x `box_rows` positions of one (batch, head), 128B swizzle.
 static int make_map(CUtensorMap* m, const void* p, const int64_t* st, int B, int H, int L, int D, int dtype,
-                    int box_rows) {
+                    int box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not available");
     return CHILL_E_CUDA;
   }
-  const cuuint64_t es = 2;
+  const cuuint64_t es = esize(dtype);
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
   const cuuint64_t row = (cuuint64_t)st[2] * es;
   cuuint64_t strides[3] = {row, H > 1 ? (cuuint64_t)st[1] * es : row * (cuuint64_t)L,
                            B > 1 ? (cuuint64_t)st[0] * es : row * (cuuint64_t)L * (cuuint64_t)H};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)(128 / es), (cuuint32_t)box_rows, 1, 1};  // 128-byte rows
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = fn(m, dtype == CHILL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                  const_cast<void*>(p), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUtensorMapDataType dt = dtype == CHILL_BF16   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : dtype == CHILL_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(m, dt, 4, const_cast<void*>(p), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return CHILL_E_CUDA;
@@ -165,9 +167,15 @@ static int make_map(CUtensorMap* m, const void* p, const int64_t* st, int B, int
     default: return CHILL_E_UNSUPPORTED;                              \
   }
 
+// fp32 tensors whose caller allowed TF32: forward on the tensor cores (fwd_tf32.cuh)
+static bool shape_tf32_ok(const chill_shape& s) {
+  if (s.flags & CHILL_FLAG_FORCE_GENERIC) return false;
+  return s.dtype == CHILL_F32 && (s.flags & CHILL_FLAG_ALLOW_TF32) && (s.D == 64 || s.D == 128) && s.sm_scale > 0.f;
+}
+
 static bool fwd_tc_eligible(const chill_fwd_args& a) {
   const chill_shape& s = a.s;
-  if (!shape_tc_ok(s)) return false;
+  if (!shape_tc_ok(s) && !shape_tf32_ok(s)) return false;
   const size_t es = esize(s.dtype);
   return tma_ok(a.q, a.q_strides, s.B, s.H, s.Lq, es) && tma_ok(a.k, a.k_strides, s.B, s.H_kv, s.Lk, es) &&
          tma_ok(a.v, a.v_strides, s.B, s.H_kv, s.Lk, es) && tma_ok(a.o, a.o_strides, s.B, s.H, s.Lq, es);
@@ -201,7 +209,11 @@ static int fwd_tc(const chill_fwd_args& a, cudaStream_t st) {
   int rc;
   if ((rc = make_map(&maps[0], a.q, a.q_strides, s.B, s.H, s.Lq, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
   if ((rc = make_map(&maps[1], a.k, a.k_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
-  if ((rc = make_map(&maps[2], a.v, a.v_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+  // V is the MN-major operand of O += P V; with 32-bit elements that takes the 128B swizzle with 32-byte atoms
+  const bool tf32 = s.dtype == CHILL_F32;
+  if ((rc = make_map(&maps[2], a.v, a.v_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, tc::kTile,
+                     tf32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B)) != CHILL_OK)
+    return rc;
   if ((rc = make_map(&maps[3], a.o, a.o_strides, s.B, s.H, s.Lq, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
   tc::FwdTcParams p;
   p.g = to_geo(s);
@@ -213,7 +225,11 @@ static int fwd_tc(const chill_fwd_args& a, cudaStream_t st) {
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
   dim3 grid((unsigned)(((s.Lq + tc::kTile - 1) / tc::kTile) * s.H * s.B), 1, 1);
   int e = 0;
-  CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_fwd<MaskT>(s.dtype, s.D, maps, p, grid, st)))
+  if (tf32) {
+    CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_fwd_tf32<MaskT>(s.D, maps, p, grid, st)))
+  } else {
+    CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_fwd<MaskT>(s.dtype, s.D, maps, p, grid, st)))
+  }
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "fwd_tc launch");
 }
 

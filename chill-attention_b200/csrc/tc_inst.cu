@@ -3,6 +3,7 @@
 #include "bwd_fused.cuh"
 #include "bwd_tc.cuh"
 #include "fwd_tc.cuh"
+#include "fwd_tf32.cuh"
 #include "tc_launch.h"
 
 #ifndef CHILL_INST_MASK
@@ -85,6 +86,31 @@ int tc_launch_fwd<InstMask>(int dtype, int D, const CUtensorMap* maps, const tc:
     if (D == 128) return launch_fwd_one<__half, 128, 1>(maps, p, grid, st);
     if (D == 64) return launch_fwd_one<__half, 64, 2>(maps, p, grid, st);
   }
+  return (int)cudaErrorInvalidValue;
+}
+
+template <int D>
+static int launch_fwd_tf32_one(const CUtensorMap* maps, const tc::FwdTcParams& p, dim3 grid, cudaStream_t st) {
+  auto kern = tc::fwd_tf32_kernel<D, InstMask>;
+  constexpr int smem = tc::FwdTf32Smem<D>::kDynamic;
+  static_assert(smem <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    configured_dev = dev;
+  }
+  kern<<<grid, tc::kFwdThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+  return (int)cudaGetLastError();
+}
+
+template <>
+int tc_launch_fwd_tf32<InstMask>(int D, const CUtensorMap* maps, const tc::FwdTcParams& p, dim3 grid, cudaStream_t st) {
+  if (D == 64) return launch_fwd_tf32_one<64>(maps, p, grid, st);
+  if (D == 128) return launch_fwd_tf32_one<128>(maps, p, grid, st);
   return (int)cudaErrorInvalidValue;
 }
 

@@ -17,6 +17,10 @@ struct BwdTcParams;
 template <class M>
 int tc_launch_fwd(int dtype, int D, const CUtensorMap* maps, const tc::FwdTcParams& p, dim3 grid, cudaStream_t st);
 
+// fp32 tensors in TF32 (fwd_tf32.cuh); maps: Q, K, V (128B swizzle with 32-byte atoms), O.
+template <class M>
+int tc_launch_fwd_tf32(int D, const CUtensorMap* maps, const tc::FwdTcParams& p, dim3 grid, cudaStream_t st);
+
 // maps: Q, K, V, dO, dQ, dK, dV.
 template <class M>
 int tc_launch_bwd(int dtype, int D, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st);

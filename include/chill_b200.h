@@ -69,6 +69,10 @@ extern "C" {
 #define CHILL_FLAG_REQUIRE_TC 2u    /* fail with CHILL_E_UNSUPPORTED instead of using the generic path */
 #define CHILL_FLAG_BWD_ONLY_DKDV 4u /* chill_bwd launches only the dK/dV kernel (per-kernel timing) */
 #define CHILL_FLAG_BWD_ONLY_DQ 8u   /* chill_bwd launches only the dQ kernel */
+#define CHILL_FLAG_ALLOW_TF32 16u   /* fp32 tensors may go through the tensor cores in TF32 (10-bit mantissa):
+                                     * chill_fwd then runs its tcgen05 kernel for head dim 64 / 128; the reference's
+                                     * precision="tf32" (chill_fwd.py:13-359, input_precision).  Without the flag fp32
+                                     * is computed in IEEE fp32 by the generic kernels. */
 
 /* The mask constants a ChillMask instance was built with (ChillMask.constargs,
  * mask.py:31-49).  Each is passed both ways: `i[n]` = the value truncated to an

@@ -216,3 +216,39 @@ def test_gradient_through_the_returned_lse(dtype, D):
         _, lse_only = ca.chill_attention(qd2, kd2, vd2, mask=mask, return_lse=True)
         (lse_only * dlse.cuda()).sum().backward()
         assert torch.isfinite(qd2.grad).all() and vd2.grad.abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("mask", big_masks(), ids=str)
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("L", [128, 700])
+def test_fp32_forward_in_tf32(mask, D, L, _lib):
+    """precision="tf32": fp32 tensors through tcgen05.mma.kind::tf32.  Stated bars: O max-abs <= 5e-3 against the
+    fp64 oracle (Q, K, V truncated to 10 mantissa bits by the tensor core, P rounded; measured 2e-3 .. 4e-3),
+    LSE <= 3e-3 * max(1, |LSE|) (measured up to 1.7e-3), gradients 5e-3 relative; the backward stays IEEE fp32."""
+    import ctypes as C
+
+    from chill_attention import _cabi, chill_attention
+
+    q, k, v, do = make_inputs(2, 4, 2, L, D, torch.float32, seed=51)
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    # the dispatch really takes the tensor-core kernel
+    a = _cabi.FwdArgs()
+    a.s = _cabi.make_shape(qd, kd, _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor], mask.constargs, None, D ** -0.5,
+                           flags=_cabi.FLAG_ALLOW_TF32)
+    o_tmp = torch.empty_like(qd)
+    a.q, a.k, a.v, a.o = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o_tmp.data_ptr()
+    for name, t in (("q_strides", qd), ("k_strides", kd), ("v_strides", vd), ("o_strides", o_tmp)):
+        setattr(a, name, (C.c_int64 * 4)(*t.stride()))
+    assert _lib.chill_fwd_uses_tensor_cores(C.byref(a)) == 1
+    o, lse = chill_attention(qd, kd, vd, mask=mask, return_lse=True, precision="tf32")
+    err = (o.detach().cpu().double() - o_ref).abs().max().item()
+    assert err <= 5e-3, f"O max-abs {err}"
+    fin = torch.isfinite(lse_ref)
+    assert torch.equal(torch.isfinite(lse.cpu()), fin)
+    lerr = ((lse.cpu().double() - lse_ref)[fin].abs() / lse_ref[fin].abs().clamp(min=1.0)).max().item()
+    assert lerr <= 3e-3, f"LSE {lerr}"
+    o.backward(do.cuda())
+    for name, got, ref in zip(("dq", "dk", "dv"), (qd.grad, kd.grad, vd.grad), g_ref):
+        rel = ((got.cpu().double() - ref).norm() / ref.norm()).item()
+        assert rel <= 5e-3, f"{name}: {rel}"  # O and LSE carry the TF32 error into the (IEEE) backward
