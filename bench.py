@@ -72,6 +72,9 @@ WORKLOADS = {
     "full": ("FullChillMask", (), "bfloat16", 8, 16, 4096, 128),
     # c2 with a quarter of the batch: same kernels and tile counts per CTA, small enough for an ncu capture
     "c2s": ("CausalChillMask", (), "bfloat16", 2, 16, 4096, 128),
+    # fp32 tensors with precision="tf32": forward on the TF32 tensor cores, backward in IEEE fp32 on the generic
+    # kernels (seconds per step: use --steps 2); the forward figure is the one of interest
+    "c2f32": ("CausalChillMask", (), "float32", 2, 16, 4096, 128),
 }
 
 
@@ -210,9 +213,10 @@ def run_ours(args):
     lse = torch.empty(B, H, L, dtype=torch.float32, device=dev)
     delta = torch.empty(B, H, L, dtype=torch.float32, device=dev)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    shape = _cabi.make_shape(q, k, functor, margs, None, scale)
-    shape_dkdv = _cabi.make_shape(q, k, functor, margs, None, scale, flags=_cabi.FLAG_BWD_ONLY_DKDV)
-    shape_dq = _cabi.make_shape(q, k, functor, margs, None, scale, flags=_cabi.FLAG_BWD_ONLY_DQ)
+    tf32 = _cabi.FLAG_ALLOW_TF32 if dtype == torch.float32 else 0  # what precision="tf32" sets for fp32 tensors
+    shape = _cabi.make_shape(q, k, functor, margs, None, scale, flags=tf32)
+    shape_dkdv = _cabi.make_shape(q, k, functor, margs, None, scale, flags=_cabi.FLAG_BWD_ONLY_DKDV | tf32)
+    shape_dq = _cabi.make_shape(q, k, functor, margs, None, scale, flags=_cabi.FLAG_BWD_ONLY_DQ | tf32)
     import ctypes as C
 
     bargs_dkdv = _cabi.backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape_dkdv)

@@ -93,13 +93,17 @@ def test_deterministic_switch_gives_bitwise_repeatable_gradients(lib):
         ca.chill_attention(qd, kd, vd, mask=mask).backward(do.cuda())
         return qd.grad, kd.grad, vd.grad
 
-    assert not ca.is_deterministic()
-    loose = grads()
-    ca.set_deterministic(True)
+    from chill_attention import _cabi
+
+    before = _cabi._deterministic  # the switch may have been set through CHILL_ATTENTION_DETERMINISTIC
     try:
+        ca.set_deterministic(False)
+        assert not ca.is_deterministic()
+        loose = grads()
+        ca.set_deterministic(True)
         a, b = grads(), grads()
     finally:
-        ca.set_deterministic(False)
+        ca.set_deterministic(before)
     for x, y in zip(a, b):
         assert torch.equal(x, y)
     for x, y in zip(loose, a):
