@@ -252,3 +252,25 @@ def test_fp32_forward_in_tf32(mask, D, L, _lib):
     for name, got, ref in zip(("dq", "dk", "dv"), (qd.grad, kd.grad, vd.grad), g_ref):
         rel = ((got.cpu().double() - ref).norm() / ref.norm()).item()
         assert rel <= 5e-3, f"{name}: {rel}"  # O and LSE carry the TF32 error into the (IEEE) backward
+
+
+def test_fp32_forward_in_tf32_with_lens_and_ragged_length(_lib):
+    """The TF32 forward with per-row valid lengths, a sequence length that is not a multiple of the tile and
+    more query heads than key heads: padded rows are exactly zero, the rest within the TF32 bars."""
+    import chill_attention as ca
+    from chill_attention import chill_attention
+
+    L, D = 333, 64
+    lens = torch.tensor([L, 1, 130, 200], dtype=torch.int32)
+    for mask in (ca.CausalChillMask(), ca.SlidingWindowChillMask(50, 7)):
+        q, k, v, do = make_inputs(4, 6, 2, L, D, torch.float32, seed=52)
+        o_ref, lse_ref, *_ = oracle_all(mask, q, k, v, do, lens)
+        o, lse = chill_attention(q.cuda(), k.cuda(), v.cuda(), mask=mask, lens=lens.cuda(), return_lse=True,
+                                 precision="tf32")
+        valid = torch.arange(L)[None, None, :] < lens.long()[:, None, None]
+        oc = o.cpu().double()
+        assert (oc[(~valid).expand(4, 6, L)] == 0).all(), "padded rows must be exactly zero"
+        assert (oc - o_ref).abs().max().item() <= 5e-3
+        fin = torch.isfinite(lse_ref)
+        assert torch.equal(torch.isfinite(lse.cpu()), fin)
+        assert ((lse.cpu().double() - lse_ref)[fin].abs() / lse_ref[fin].abs().clamp(min=1.0)).max().item() <= 3e-3
