@@ -131,7 +131,8 @@ typedef struct chill_bwd_args {
    * per-key-tile contributions to dQ are summed in this buffer with fp32 reductions, whose order is not
    * fixed, so dQ may differ in its last bits from run to run (dK and dV do not).  Without it chill_bwd runs
    * the deterministic two-kernel backward, which is also what the reference's accumulation order
-   * (chill_bwd_dq.py:300-394: one program owns a query tile) corresponds to. */
+   * (chill_bwd_dq.py:300-394: one program owns a query tile) corresponds to.  The call zero-fills the buffer on
+   * the given stream before use; two calls that can overlap on the GPU need a buffer each. */
   float* dq_accum;
   /* Optional (may be NULL): gradient of the loss with respect to the LSE that chill_fwd returned (log2 units,
    * same layout rules as lse).  chill_bwd_delta folds it into delta (delta -= log2(e) * d_lse), which is all the
