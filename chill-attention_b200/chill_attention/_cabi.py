@@ -32,13 +32,13 @@ BUILTIN_FUNCTOR_IDS = {
 
 _DTYPES = {torch.float32: CHILL_F32, torch.float16: CHILL_F16, torch.bfloat16: CHILL_BF16}
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 EXPORTS = (
     "chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_bwd_scratch_bytes", "chill_bwd_dq_accum_bytes",
     "chill_fwd_uses_tensor_cores",
     "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits", "chill_read_device_status",
-    "chill_abi_version", "chill_status_string", "chill_last_cuda_error",
+    "chill_launch_count", "chill_abi_version", "chill_status_string", "chill_last_cuda_error",
 )
 
 
@@ -70,7 +70,8 @@ class BwdArgs(C.Structure):
                 ("dk", C.c_void_p), ("dv", C.c_void_p), ("q_strides", _S4), ("k_strides", _S4), ("v_strides", _S4),
                 ("o_strides", _S4), ("do_strides", _S4), ("dq_strides", _S4), ("dk_strides", _S4),
                 ("dv_strides", _S4), ("lse_strides", _S3), ("dq_accum", C.c_void_p), ("d_lse", C.c_void_p),
-                ("dlse_strides", _S3)]
+                ("dlse_strides", _S3), ("dk_part", C.c_void_p), ("dv_part", C.c_void_p), ("part_strides", _S3),
+                ("part_head", C.c_int32), ("part_tail", C.c_int32)]
 
 
 class ChillLibraryError(RuntimeError):
@@ -109,6 +110,7 @@ def load_library(path: str | None = None) -> C.CDLL:
         lib.chill_status_string.argtypes = [C.c_int]
         lib.chill_status_string.restype = C.c_char_p
         lib.chill_last_cuda_error.restype = C.c_char_p
+        lib.chill_launch_count.restype = C.c_ulonglong
         for name in ("chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_fwd_uses_tensor_cores",
                      "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits",
                      "chill_read_device_status", "chill_abi_version"):
@@ -172,7 +174,7 @@ def forward(lib, q, k, v, o, lse, shape: Shape):
     check(lib, lib.chill_fwd(C.byref(a), _stream()), "chill_fwd")
 
 
-def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None, d_lse=None) -> BwdArgs:
+def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None, d_lse=None, part=None) -> BwdArgs:
     a = BwdArgs()
     a.s = shape
     a.q, a.k, a.v, a.o, a.d_o = (t.data_ptr() for t in (q, k, v, o, do))
@@ -185,6 +187,15 @@ def backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum
     if d_lse is not None:  # gradient of the loss w.r.t. the returned LSE (log2 units), fp32 [B, H, L]
         a.d_lse = d_lse.data_ptr()
         a.dlse_strides = _strides(d_lse, 3)
+    if part is not None:
+        # (dk_part, dv_part, head, tail): fp32 [B, H_kv, head + tail, D] views (any batch / head / row strides,
+        # contiguous channels) that receive the un-rounded dK / dV of the first `head` and last `tail` key rows
+        dk_part, dv_part, head, tail = part
+        if dk_part.dtype != torch.float32 or dk_part.stride() != dv_part.stride() or dk_part.stride(3) != 1:
+            raise ValueError("partial dK / dV outputs must be fp32 with equal strides and contiguous channels")
+        a.dk_part, a.dv_part = dk_part.data_ptr(), dv_part.data_ptr()
+        a.part_strides = (C.c_int64 * 3)(*dk_part.stride()[:3])
+        a.part_head, a.part_tail = head, tail
     return a
 
 
@@ -214,11 +225,20 @@ def dq_accum_for(lib, a: BwdArgs, device):
     return torch.empty(nbytes // 4, dtype=torch.float32, device=device)
 
 
+def tma_compatible(t) -> bool:
+    """What the tensor-core kernels need of a [B, H, L, D] operand: contiguous channels, no broadcast
+    (zero-stride) dimension, 16-byte aligned base and batch / head / row strides."""
+    es = t.element_size()
+    if t.stride(-1) != 1 or t.data_ptr() % 16:
+        return False
+    return all(st > 0 and (st * es) % 16 == 0 for st, n in zip(t.stride()[:-1], t.shape[:-1]) if n > 1)
+
+
 def backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape: Shape, dq_accum=None, deterministic=False,
-             d_lse=None):
+             d_lse=None, part=None):
     """chill_bwd_delta + chill_bwd.  Without `dq_accum` the fp32 dQ scratch of the single-kernel backward is
     allocated here when the call can use it; `deterministic=True` forces the two-kernel form."""
-    a = backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape, dq_accum, d_lse)
+    a = backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape, dq_accum, d_lse, part)
     if dq_accum is None and not deterministic:
         dq_accum = dq_accum_for(lib, a, q.device)  # stays referenced until the launches are enqueued
         a.dq_accum = dq_accum.data_ptr() if dq_accum is not None else None

@@ -30,6 +30,43 @@ from .mask import ChillMask
 logger = logging.getLogger(__name__)
 
 _HEAD_DIMS = {16, 32, 64, 128, 256}
+#: how many backward calls each kernel family served (read by tests; see backward_path_counts)
+_BWD_PATHS = {"tensor_core": 0, "generic": 0}
+
+
+def backward_path_counts() -> dict:
+    """Copy of the per-process counters of backward calls served by the tensor-core and by the generic kernels."""
+    return dict(_BWD_PATHS)
+
+
+def _backward_operand(do: torch.Tensor) -> torch.Tensor:
+    """The incoming gradient as the kernels want it.  Autograd often hands over an expanded tensor (all strides 0
+    after ``o.sum().backward()``) or a transposed view; the tensor-core kernels cannot describe those to TMA and
+    the call would otherwise be served by the ~1000x slower generic kernels.  One L x D copy fixes that (the
+    reference asserts ``do.stride(-1) == 1`` at this point, chill.py:270)."""
+    return do if _cabi.tma_compatible(do) else do.contiguous()
+
+
+def _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scale, d_lse=None):
+    import ctypes as C
+
+    with torch.cuda.device(q.device):
+        do = _backward_operand(do)
+        delta = torch.empty(o.shape[:-1], dtype=torch.float32, device=o.device)
+        DQ = torch.empty_like(q, memory_format=torch.contiguous_format)
+        DK = torch.empty_like(k, memory_format=torch.contiguous_format)
+        DV = torch.empty_like(v, memory_format=torch.contiguous_format)
+        lens_c = lens.contiguous() if lens is not None else None
+        shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale)
+        a = _cabi.backward_args(q, k, v, o, do, lse, delta, DQ, DK, DV, shape, None, d_lse)
+        tc = lib.chill_bwd_uses_tensor_cores(C.byref(a)) == 1
+        _BWD_PATHS["tensor_core" if tc else "generic"] += 1
+        accum = _cabi.dq_accum_for(lib, a, q.device) if tc else None
+        a.dq_accum = accum.data_ptr() if accum is not None else None
+        st = _cabi._stream()
+        _cabi.check(lib, lib.chill_bwd_delta(C.byref(a), st), "chill_bwd_delta")
+        _cabi.check(lib, lib.chill_bwd(C.byref(a), st), "chill_bwd")
+    return DQ, DK, DV
 #: mask class name -> (library, functor id); filled by register_chill_mask
 _REGISTRY: dict[str, tuple] = {}
 
@@ -122,15 +159,7 @@ def register_chill_mask(mask: ChillMask):
         precision: str,
         autotune: bool,
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        with torch.cuda.device(q.device):
-            delta = torch.empty(o.shape[:-1], dtype=torch.float32, device=o.device)
-            DQ = torch.empty_like(q, memory_format=torch.contiguous_format)
-            DK = torch.empty_like(k, memory_format=torch.contiguous_format)
-            DV = torch.empty_like(v, memory_format=torch.contiguous_format)
-            lens_c = lens.contiguous() if lens is not None else None
-            shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale)
-            _cabi.backward(lib, q, k, v, o, do, lse, delta, DQ, DK, DV, shape)
-        return DQ, DK, DV
+        return _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scale)
 
     @torch.library.register_fake(f"chill_attention::backward{mask_name}")
     def attention_backward_adapter_abstract(q, k, v, lens, o, lse, do, mask_args, sm_scale, prescale_qk, precision,
@@ -158,15 +187,7 @@ def register_chill_mask(mask: ChillMask):
         mask_args: typing.List[typing.Union[int, float, bool]],
         sm_scale: float,
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        with torch.cuda.device(q.device):
-            delta = torch.empty(o.shape[:-1], dtype=torch.float32, device=o.device)
-            DQ = torch.empty_like(q, memory_format=torch.contiguous_format)
-            DK = torch.empty_like(k, memory_format=torch.contiguous_format)
-            DV = torch.empty_like(v, memory_format=torch.contiguous_format)
-            lens_c = lens.contiguous() if lens is not None else None
-            shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale)
-            _cabi.backward(lib, q, k, v, o, do.contiguous(), lse, delta, DQ, DK, DV, shape, d_lse=dlse.float())
-        return DQ, DK, DV
+        return _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scale, d_lse=dlse.float())
 
     @torch.library.register_fake(f"chill_attention::backward_with_dlse{mask_name}")
     def attention_backward_dlse_adapter_abstract(q, k, v, lens, o, lse, do, dlse, mask_args, sm_scale):
@@ -207,26 +228,25 @@ def register_chill_mask(mask: ChillMask):
 
 
 def _chill_reference_naive(mask: ChillMask, q, k, v, lens):
-    """Dense-mask PyTorch attention used for testing (reference: chill.py:498-544).
-
-    Returns ``(output * res_mask, res_mask)``; rows at or beyond ``lens[b]`` are zeroed.
-    """
-    import torch.nn.functional as F
-
-    assert q.size(2) == k.size(2)
-    if q.shape[1] != k.shape[1]:
-        group = q.shape[1] // k.shape[1]
-        k = k.repeat_interleave(group, dim=1)
-        v = v.repeat_interleave(group, dim=1)
-    T = q.size(2)
-    attn_mask = mask.make_mask(T, device=q.device)
+    """Dense-mask attention in plain PyTorch, for tests (same contract as the reference's helper of this name,
+    chill.py:498-544): returns ``(output * row_mask, row_mask)`` where ``row_mask`` zeroes query rows at or beyond
+    ``lens[b]`` (a 0-dim 1 when ``lens`` is None).  Keys at or beyond ``lens[b]`` are never attended.
+    Scores are scaled by head_dim ** -0.5; a row that sees no key yields zeros."""
+    B, H, T, D = q.shape
+    assert k.shape[2] == T and v.shape[2] == T
+    groups = H // k.shape[1]
+    if groups > 1:  # grouped-query attention: every kv head serves `groups` consecutive query heads
+        k, v = (t[:, :, None].expand(B, t.shape[1], groups, T, D).reshape(B, H, T, D) for t in (k, v))
+    visible = mask.make_mask(T, device=q.device)[None, None]  # [1, 1, T, T]
+    row_mask = torch.ones((), dtype=torch.bool, device=q.device)
     if lens is not None:
-        keep = (torch.arange(T, device=q.device).unsqueeze(0) < lens.unsqueeze(-1)).unsqueeze(-1)
-        attn_mask = attn_mask.unsqueeze(0).unsqueeze(0) & (keep & keep.transpose(-1, -2)).unsqueeze(1)
-        res_mask = keep.unsqueeze(1)
-    else:
-        res_mask = torch.as_tensor(1, device=q.device)
-    return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask) * res_mask, res_mask
+        inside = torch.arange(T, device=q.device)[None, :] < lens[:, None]  # [B, T]
+        visible = visible & inside[:, None, None, :] & inside[:, None, :, None]
+        row_mask = inside[:, None, :, None]
+    scores = torch.matmul(q, k.transpose(-1, -2)) * (D ** -0.5)
+    scores = scores.masked_fill(~visible, float("-inf"))
+    probs = torch.softmax(scores.float(), dim=-1).nan_to_num(0.0).to(q.dtype)  # all -inf row -> zeros
+    return torch.matmul(probs, v) * row_mask, row_mask
 
 
 def _chill_attention(q, k, v, lens, mask_name, mask_args, sm_scale, return_lse, prescale_qk, precision, autotune):

@@ -19,10 +19,6 @@ exercised on CPU ranks (gloo) with any dense implementation.
 """
 from __future__ import annotations
 
-import json
-import os
-import time
-
 import torch
 import torch.distributed as dist
 
@@ -67,81 +63,114 @@ def _peer(group):
     return (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
 
 
-def start_halo_exchange(k_local, v_local, left: int, right: int, group=None):
-    """Post the K/V halo sends and receives (asynchronous).  Returns (works, recv_left, recv_right, hl, hr):
-    ``recv_left`` = [2, B, H, hl, D] buffer for the last ``left`` rows of rank-1 (K then V), ``recv_right`` the
-    first ``right`` rows of rank+1; hl / hr are 0 at the ends of the sequence.  Wait on ``works`` before
-    reading the buffers."""
+class HaloBuffer:
+    """A rank's shard of K or V with spare rows in front of and behind it for the neighbours' halo rows.
+
+    Memory order is [batch][position][head][channel], so the halo rows of all heads of one batch row are one
+    contiguous block: the NCCL receive writes them straight into place and the send reads the shard's own
+    first / last rows in place - no staging copy on either side.  ``local`` is the [B, H, Ls, D] view the
+    attention call takes as k or v (fill it, or have the projection write into it); ``rows(lo, hi)`` is the
+    same kind of view over positions lo..hi relative to the shard's first row (negative = left halo).
+    The kernels read such views through their strides (TMA descriptors), no copy is made.
+    """
+
+    def __init__(self, B, H, Ls, D, left, right, dtype, device):
+        self.B, self.H, self.Ls, self.D, self.left, self.right = B, H, Ls, D, int(left), int(right)
+        self.storage = torch.empty((B, self.left + Ls + self.right, H, D), dtype=dtype, device=device)
+
+    @classmethod
+    def like(cls, t, left, right):
+        """A buffer for a [B, H, Ls, D] tensor ``t`` with the tensor copied into ``local``."""
+        B, H, Ls, D = t.shape
+        buf = cls(B, H, Ls, D, left, right, t.dtype, t.device)
+        buf.local.copy_(t.detach())
+        return buf
+
+    def seq_rows(self, lo, hi):
+        """[B, hi - lo, H, D] in memory order (contiguous per batch row)."""
+        return self.storage[:, self.left + lo:self.left + hi]
+
+    def rows(self, lo, hi):
+        return self.seq_rows(lo, hi).permute(0, 2, 1, 3)
+
+    @property
+    def local(self):
+        return self.rows(0, self.Ls)
+
+
+def _per_batch(t):
+    """Contiguous pieces of a [B, rows, H, D] view whose batch rows are each contiguous."""
+    return [t] if t.is_contiguous() else [t[b] for b in range(t.shape[0])]
+
+
+def start_halo_exchange(kbuf: HaloBuffer, vbuf: HaloBuffer, left: int, right: int, group=None):
+    """Post the K/V halo sends and receives (asynchronous) between neighbouring ranks: the last ``left`` rows of
+    every shard go to rank+1's left spare rows, the first ``right`` rows to rank-1's right spare rows.  Returns
+    (works, hl, hr): the number of halo rows this rank receives on each side (0 at the ends of the sequence).
+    Wait on ``works`` before reading the spare rows."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     hl = left if rank > 0 else 0
     hr = right if rank < world - 1 else 0
-    B, H, Ls, D = k_local.shape
-    ops, recv_l, recv_r = [], None, None
+    Ls = kbuf.Ls
+    ops = []
     peer = _peer(group)
-    if rank < world - 1 and left > 0:  # my tail is the right neighbour's left halo
-        tail = torch.stack([k_local[:, :, Ls - left:], v_local[:, :, Ls - left:]]).contiguous()
-        ops.append(dist.P2POp(dist.isend, tail, peer(rank + 1), group))
-    if rank > 0 and right > 0:
-        head = torch.stack([k_local[:, :, :right], v_local[:, :, :right]]).contiguous()
-        ops.append(dist.P2POp(dist.isend, head, peer(rank - 1), group))
-    if hl > 0:
-        recv_l = torch.empty((2, B, H, hl, D), dtype=k_local.dtype, device=k_local.device)
-        ops.append(dist.P2POp(dist.irecv, recv_l, peer(rank - 1), group))
-    if hr > 0:
-        recv_r = torch.empty((2, B, H, hr, D), dtype=k_local.dtype, device=k_local.device)
-        ops.append(dist.P2POp(dist.irecv, recv_r, peer(rank + 1), group))
+    for buf in (kbuf, vbuf):  # the same order on both sides of every pair: K pieces, then V pieces
+        if rank < world - 1 and left > 0:  # my tail is the right neighbour's left halo
+            ops += [dist.P2POp(dist.isend, t, peer(rank + 1), group) for t in _per_batch(buf.seq_rows(Ls - left, Ls))]
+        if rank > 0 and right > 0:
+            ops += [dist.P2POp(dist.isend, t, peer(rank - 1), group) for t in _per_batch(buf.seq_rows(0, right))]
+        if hl > 0:
+            ops += [dist.P2POp(dist.irecv, t, peer(rank - 1), group) for t in _per_batch(buf.seq_rows(-hl, 0))]
+        if hr > 0:
+            ops += [dist.P2POp(dist.irecv, t, peer(rank + 1), group) for t in _per_batch(buf.seq_rows(Ls, Ls + hr))]
     works = dist.batch_isend_irecv(ops) if ops else []
-    return works, recv_l, recv_r, hl, hr
+    return works, hl, hr
 
 
-def exchange_halo_grads(dk_halo_left, dk_halo_right, left: int, right: int, like, group=None):
-    """Send the dK/dV rows computed for halo keys back to their owners; receive what the neighbours
-    computed for this rank's boundary rows.  ``dk_halo_left`` / ``dk_halo_right``: [2, B, H, hl|hr, D] or None.
-    Returns (from_right, from_left): [2, B, H, left, D] to add to the last ``left`` local rows, and
-    [2, B, H, right, D] to add to the first ``right`` rows (None where there is no neighbour)."""
+def start_halo_grad_exchange(part_left, hl, part_right, hr, left, right, like, group=None, dtype=torch.float32):
+    """Post the return of the dK/dV rows computed for halo keys to their owners, in fp32 (asynchronous).
+    ``part_left`` / ``part_right``: [2 (dK, dV), B, rows, H_kv, D] fp32 partial results of the boundary calls,
+    whose first ``hl`` / last ``hr`` rows belong to the neighbours.  Returns (works, from_right, from_left):
+    [2, B, left, H_kv, D] to add to this rank's last ``left`` key rows and [2, B, right, H_kv, D] for its first
+    ``right`` rows (None where there is no neighbour)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
-    B, H, _, D = like.shape
+    B, Hkv, _, D = like.shape
     ops, from_right, from_left = [], None, None
     peer = _peer(group)
-    if dk_halo_left is not None:
-        ops.append(dist.P2POp(dist.isend, dk_halo_left.contiguous(), peer(rank - 1), group))
-    if dk_halo_right is not None:
-        ops.append(dist.P2POp(dist.isend, dk_halo_right.contiguous(), peer(rank + 1), group))
     if rank < world - 1 and left > 0:  # the right neighbour used my last `left` rows as its left halo
-        from_right = torch.empty((2, B, H, left, D), dtype=like.dtype, device=like.device)
-        ops.append(dist.P2POp(dist.irecv, from_right, peer(rank + 1), group))
+        from_right = torch.empty((2, B, left, Hkv, D), dtype=dtype, device=like.device)
     if rank > 0 and right > 0:
-        from_left = torch.empty((2, B, H, right, D), dtype=like.dtype, device=like.device)
-        ops.append(dist.P2POp(dist.irecv, from_left, peer(rank - 1), group))
-    for w in (dist.batch_isend_irecv(ops) if ops else []):
-        w.wait()
-    return from_right, from_left
+        from_left = torch.empty((2, B, right, Hkv, D), dtype=dtype, device=like.device)
+    for t in range(2):
+        if hl > 0:
+            ops += [dist.P2POp(dist.isend, part_left[t, b, :hl], peer(rank - 1), group) for b in range(B)]
+        if hr > 0:
+            n = part_right.shape[2]
+            ops += [dist.P2POp(dist.isend, part_right[t, b, n - hr:], peer(rank + 1), group) for b in range(B)]
+        if from_right is not None:
+            ops += [dist.P2POp(dist.irecv, from_right[t, b], peer(rank + 1), group) for b in range(B)]
+        if from_left is not None:
+            ops += [dist.P2POp(dist.irecv, from_left[t, b], peer(rank - 1), group) for b in range(B)]
+    works = dist.batch_isend_irecv(ops) if ops else []
+    return works, from_right, from_left
 
 
 # ------------------------------------------------------------------ local kernels (C ABI)
-def cabi_local_forward(mask, q, k_ext, v_ext, q_offset, k_offset, seq_len, sm_scale, o=None, lse=None):
-    """O, LSE of local query rows against local key rows with global offsets.  ``o`` / ``lse`` may be views
-    of larger buffers (row slices); they are written in place."""
+def cabi_local_forward(mask, q, k_ext, v_ext, q_offset, k_offset, seq_len, sm_scale, o, lse):
+    """O, LSE of local query rows against local key rows with global offsets, written into ``o`` / ``lse``
+    (which may be row slices of larger buffers)."""
     lib, functor = _library_for(mask)
-    if o is None:
-        o = torch.empty_like(q, memory_format=torch.contiguous_format)
-    if lse is None:
-        lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
     shape = _cabi.make_shape(q, k_ext, functor, mask.constargs, None, sm_scale, q_offset, k_offset, seq_len)
     _cabi.forward(lib, q, k_ext, v_ext, o, lse, shape)
-    return o, lse
 
 
-def cabi_local_backward(mask, q, k_ext, v_ext, o, lse, do, q_offset, k_offset, seq_len, sm_scale, dq=None):
+def cabi_local_backward(mask, q, k_ext, v_ext, o, lse, do, q_offset, k_offset, seq_len, sm_scale, dq, dk, dv, part):
+    """dQ (into ``dq``), 16-bit dK / dV (into ``dk`` / ``dv``) and, when ``part`` = (dk_part, dv_part, head, tail)
+    is given, the un-rounded fp32 dK / dV of the first ``head`` and last ``tail`` key rows."""
     lib, functor = _library_for(mask)
-    if dq is None:
-        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
-    dk = torch.empty_like(k_ext, memory_format=torch.contiguous_format)
-    dv = torch.empty_like(v_ext, memory_format=torch.contiguous_format)
     delta = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
     shape = _cabi.make_shape(q, k_ext, functor, mask.constargs, None, sm_scale, q_offset, k_offset, seq_len)
-    _cabi.backward(lib, q, k_ext, v_ext, o, do, lse, delta, dq, dk, dv, shape)
-    return dq, dk, dv
+    _cabi.backward(lib, q, k_ext, v_ext, o, do, lse, delta, dq, dk, dv, shape, part=part)
 
 
 def _library_for(mask):
@@ -157,175 +186,174 @@ def _regions(Ls, hl, hr, left, right):
     boundary rows that need the right halo; and the local key rows each boundary part can see."""
     bl = left if hl > 0 else 0
     br = right if hr > 0 else 0
-    if bl + br > Ls:  # tiny shard: treat every row as boundary-left (keys = halo_left + local + halo_right)
+    if bl + br > Ls:  # tiny shard: treat every row as boundary (keys = halo_left + local + halo_right)
         return None
     return {"bl": bl, "br": br, "kl_hi": min(Ls, bl + right), "kr_lo": max(0, Ls - br - left)}
 
 
-def _call_fwd(fn, o, lse, mask, q, k, v, q_off, k_off, seq_len, sm_scale):
-    """Run a local forward into the views ``o`` / ``lse`` (callbacks without out-parameters are copied)."""
-    try:
-        ro, rl = fn(mask, q, k, v, q_off, k_off, seq_len, sm_scale, o=o, lse=lse)
-    except TypeError:
-        ro, rl = fn(mask, q, k, v, q_off, k_off, seq_len, sm_scale)
-    if ro.data_ptr() != o.data_ptr():
-        o.copy_(ro)
-        lse.copy_(rl)
+def _calls(Ls, hl, hr, left, right):
+    """The local attention calls of one shard as (kind, first query row, end query row, first key row, end key
+    row), rows relative to the shard's first position (key rows < 0 or >= Ls are halo rows)."""
+    reg = _regions(Ls, hl, hr, left, right)
+    if reg is None:
+        return [("boundary", 0, Ls, -hl, Ls + hr)]
+    calls = []
+    if reg["bl"] > 0:
+        calls.append(("boundary", 0, reg["bl"], -hl, reg["kl_hi"]))
+    if reg["br"] > 0:
+        calls.append(("boundary", Ls - reg["br"], Ls, reg["kr_lo"], Ls + hr))
+    if Ls - reg["br"] > reg["bl"]:
+        calls.append(("interior", reg["bl"], Ls - reg["br"], 0, Ls))
+    return calls
 
 
 class _SequenceShardedAttention(torch.autograd.Function):
     """Forward: post the halo exchange, run the interior rows (which see local keys only) while it is in
-    flight, then the boundary rows against [halo | the few local rows they can see].  Backward mirrors it and
-    returns the halo keys' dK/dV to their owners.  No full-size copy of K/V is ever made."""
+    flight, then the boundary rows against views of [halo | the local rows they can see].  Backward: the
+    boundary rows first, so that the dK/dV they produce for halo keys travel back to their owners (in fp32)
+    while the interior rows run; every key row that receives more than one contribution is summed in fp32 and
+    rounded once.  No copy of K or V is made when they live in HaloBuffers."""
 
     @staticmethod
-    def forward(ctx, q, k, v, mask, seq_len, sm_scale, group, local_forward, local_backward):
-        rank = dist.get_rank(group)
+    def forward(ctx, q, k, v, mask, seq_len, sm_scale, group, local_forward, local_backward, halo_buffers):
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
         B, H, Ls, D = q.shape
         left, right = halo_sizes(mask, Ls)
-        works, recv_l, recv_r, hl, hr = start_halo_exchange(k, v, left, right, group)
-        reg = _regions(Ls, hl, hr, left, right)
+        cap_l = left if rank > 0 else 0
+        cap_r = right if rank < world - 1 else 0
+        if halo_buffers is None:
+            kbuf, vbuf = HaloBuffer.like(k, cap_l, cap_r), HaloBuffer.like(v, cap_l, cap_r)
+        else:
+            kbuf, vbuf = halo_buffers
+            for buf, t in ((kbuf, k), (vbuf, v)):
+                if buf.local.data_ptr() != t.data_ptr() or buf.local.shape != t.shape or buf.local.stride() != t.stride():
+                    raise ValueError("halo_buffers must be the HaloBuffers whose .local views were passed as k and v")
+                if buf.left < cap_l or buf.right < cap_r:
+                    raise ValueError(f"HaloBuffer has ({buf.left}, {buf.right}) spare rows, the mask needs ({cap_l}, {cap_r})")
+        works, hl, hr = start_halo_exchange(kbuf, vbuf, left, right, group)
         base = rank * Ls
         o = torch.empty((B, H, Ls, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, H, Ls), dtype=torch.float32, device=q.device)
-        parts = []  # (row slice, k tensor, v tensor, k_offset, halo rows in front, halo rows behind)
-        if reg is not None:
-            bl, br = reg["bl"], reg["br"]
-            if Ls - br > bl:  # interior first: independent of the exchange
-                sl = slice(bl, Ls - br)
-                _call_fwd(local_forward, o[:, :, sl], lse[:, :, sl], mask, q[:, :, sl], k, v, base + bl, base, seq_len, sm_scale)
-                parts.append((sl, None, None, base, 0, 0))
-        for w in works:
-            w.wait()
-        if reg is None:
-            pieces_k = ([recv_l[0]] if hl else []) + [k] + ([recv_r[0]] if hr else [])
-            pieces_v = ([recv_l[1]] if hl else []) + [v] + ([recv_r[1]] if hr else [])
-            k_ext, v_ext = torch.cat(pieces_k, dim=2), torch.cat(pieces_v, dim=2)
-            _call_fwd(local_forward, o, lse, mask, q, k_ext, v_ext, base, base - hl, seq_len, sm_scale)
-            parts.append((slice(0, Ls), k_ext, v_ext, base - hl, hl, hr))
-        else:
-            if reg["bl"] > 0:
-                k_b = torch.cat([recv_l[0], k[:, :, :reg["kl_hi"]]], dim=2)
-                v_b = torch.cat([recv_l[1], v[:, :, :reg["kl_hi"]]], dim=2)
-                sl = slice(0, reg["bl"])
-                _call_fwd(local_forward, o[:, :, sl], lse[:, :, sl], mask, q[:, :, sl], k_b, v_b, base, base - hl, seq_len, sm_scale)
-                parts.append((sl, k_b, v_b, base - hl, hl, 0))
-            if reg["br"] > 0:
-                k_b = torch.cat([k[:, :, reg["kr_lo"]:], recv_r[0]], dim=2)
-                v_b = torch.cat([v[:, :, reg["kr_lo"]:], recv_r[1]], dim=2)
-                sl = slice(Ls - reg["br"], Ls)
-                _call_fwd(local_forward, o[:, :, sl], lse[:, :, sl], mask, q[:, :, sl], k_b, v_b, base + Ls - reg["br"],
-                          base + reg["kr_lo"], seq_len, sm_scale)
-                parts.append((sl, k_b, v_b, base + reg["kr_lo"], 0, hr))
+        calls = _calls(Ls, hl, hr, left, right)
+        waited = False
+        for kind, q0, q1, k0, k1 in sorted(calls, key=lambda c: c[0] != "interior"):  # interior first
+            if kind != "interior" and not waited:
+                for w in works:
+                    w.wait()
+                waited = True
+            local_forward(mask, q[:, :, q0:q1], kbuf.rows(k0, k1), vbuf.rows(k0, k1), base + q0, base + k0, seq_len,
+                          sm_scale, o=o[:, :, q0:q1], lse=lse[:, :, q0:q1])
+        if not waited:
+            for w in works:
+                w.wait()
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.parts = parts
-        ctx.cfg = (mask, seq_len, sm_scale, group, local_backward, hl, hr, left, right, base, reg)
+        ctx.bufs = (kbuf, vbuf)
+        ctx.cfg = (mask, seq_len, sm_scale, group, local_backward, hl, hr, left, right, base, calls)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
-        mask, seq_len, sm_scale, group, local_backward, hl, hr, left, right, base, reg = ctx.cfg
+        kbuf, vbuf = ctx.bufs
+        mask, seq_len, sm_scale, group, local_backward, hl, hr, left, right, base, calls = ctx.cfg
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
         B, H, Ls, D = q.shape
+        Hkv = k.shape[1]
+        dev = q.device
+        acc_dtype = torch.float64 if k.dtype == torch.float64 else torch.float32
         do = do.contiguous()
-        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
-        dk = dv = None
-        small = []  # (dk_part, dv_part, first local key row, halo rows in front, halo rows behind)
-        for sl, k_b, v_b, k_off, h_front, h_back in ctx.parts:
-            qs, os_, ls, dos = q[:, :, sl], o[:, :, sl], lse[:, :, sl], do[:, :, sl]
-            kk, vv = (k, v) if k_b is None else (k_b, v_b)
-            q_off = base + sl.start
-            try:
-                rdq, rdk, rdv = local_backward(mask, qs, kk, vv, os_, ls, dos, q_off, k_off, seq_len, sm_scale, dq=dq[:, :, sl])
-            except TypeError:
-                rdq, rdk, rdv = local_backward(mask, qs, kk, vv, os_, ls, dos, q_off, k_off, seq_len, sm_scale)
-            if rdq.data_ptr() != dq[:, :, sl].data_ptr():
-                dq[:, :, sl].copy_(rdq)
-            if k_b is None:  # interior: its dK/dV cover every local key row and become the result buffers
-                dk, dv = rdk, rdv
+        # Gradients in the memory order of their tensors (a dense K / V view of a HaloBuffer is position-major):
+        # autograd then accumulates them as they are instead of re-laying them out with a strided copy.
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        interior = [c for c in calls if c[0] == "interior"]
+        boundary = [c for c in calls if c[0] != "interior"]
+        # Key rows that get more than one contribution (this rank's boundary and interior calls, the neighbours'
+        # boundary calls) are summed in fp32: the first `hd` and the last `tl` rows of the shard.
+        hd = max([c[4] for c in boundary if c[3] <= 0] + [right if rank > 0 else 0] + [0])
+        tl = max([Ls - max(c[3], 0) for c in boundary if c[4] >= Ls and c[3] > 0] + [left if rank < world - 1 else 0] + [0])
+        hd, tl = min(hd, Ls), min(tl, Ls)
+        if not interior or hd + tl > Ls:
+            hd, tl = Ls, 0
+        acc = None
+
+        def run(call, part_buf, head, tail):
+            _, q0, q1, k0, k1 = call
+            part = (part_buf[0].permute(0, 2, 1, 3), part_buf[1].permute(0, 2, 1, 3), head, tail)
+            if call[0] == "interior":
+                dkc, dvc = dk, dv  # the 16-bit results of the rows in between are final
             else:
-                small.append((rdk, rdv, k_off + h_front - base, h_front, h_back))
-        if dk is None:
-            dk, dv = torch.zeros_like(k, memory_format=torch.contiguous_format), torch.zeros_like(v, memory_format=torch.contiguous_format)
-        send_l = send_r = None
-        for rdk, rdv, row0, h_front, h_back in small:
-            n_local = rdk.shape[2] - h_front - h_back
-            dk[:, :, row0:row0 + n_local] += rdk[:, :, h_front:h_front + n_local]
-            dv[:, :, row0:row0 + n_local] += rdv[:, :, h_front:h_front + n_local]
-            if h_front:
-                send_l = torch.stack([rdk[:, :, :h_front], rdv[:, :, :h_front]])
-            if h_back:
-                send_r = torch.stack([rdk[:, :, h_front + n_local:], rdv[:, :, h_front + n_local:]])
-        from_right, from_left = exchange_halo_grads(send_l, send_r, left, right, dk, group)
+                dkc = torch.empty((B, Hkv, k1 - k0, D), dtype=k.dtype, device=dev)
+                dvc = torch.empty_like(dkc)
+            local_backward(mask, q[:, :, q0:q1], kbuf.rows(k0, k1), vbuf.rows(k0, k1), o[:, :, q0:q1], lse[:, :, q0:q1],
+                           do[:, :, q0:q1], base + q0, base + k0, seq_len, sm_scale, dq=dq[:, :, q0:q1], dk=dkc, dv=dvc,
+                           part=part)
+
+        parts = []  # (fp32 [2, B, rows, Hkv, D], first key row relative to the shard)
+        part_left = part_right = None
+        for call in boundary:
+            _, q0, q1, k0, k1 = call
+            buf = torch.empty((2, B, k1 - k0, Hkv, D), dtype=acc_dtype, device=dev)
+            run(call, buf, k1 - k0, 0)
+            parts.append((buf, k0))
+            if k0 < 0:
+                part_left = buf
+            if k1 > Ls:
+                part_right = buf
+        works, from_right, from_left = start_halo_grad_exchange(part_left, hl, part_right, hr, left, right, k, group, acc_dtype)
+        if hd + tl > 0:
+            if interior:
+                acc = torch.empty((2, B, hd + tl, Hkv, D), dtype=acc_dtype, device=dev)
+                run(interior[0], acc, hd, tl)
+            else:
+                acc = torch.zeros((2, B, hd + tl, Hkv, D), dtype=acc_dtype, device=dev)
+        elif interior:
+            run(interior[0], torch.empty((2, B, 0, Hkv, D), dtype=acc_dtype, device=dev), 0, 0)
+
+        def add_rows(t, row0):
+            """acc += t for the shard's key rows [row0, row0 + rows of t) that lie inside it."""
+            n = t.shape[2]
+            lo, hi = max(row0, 0), min(row0 + n, Ls)
+            done = 0
+            a, b = lo, min(hi, hd)  # part in the head region
+            if b > a:
+                acc[:, :, a:b] += t[:, :, a - row0:b - row0]
+                done += b - a
+            a, b = max(lo, Ls - tl), hi  # part in the tail region
+            if b > a:
+                acc[:, :, hd + a - (Ls - tl):hd + b - (Ls - tl)] += t[:, :, a - row0:b - row0]
+                done += b - a
+            assert done == max(hi - lo, 0), "a partial dK/dV row has no fp32 accumulator"
+
+        for buf, k0 in parts:
+            add_rows(buf, k0)
+        for w in works:
+            w.wait()
         if from_right is not None:
-            dk[:, :, Ls - left:] += from_right[0]
-            dv[:, :, Ls - left:] += from_right[1]
+            add_rows(from_right, Ls - left)
         if from_left is not None:
-            dk[:, :, :right] += from_left[0]
-            dv[:, :, :right] += from_left[1]
-        return dq, dk, dv, None, None, None, None, None, None
+            add_rows(from_left, 0)
+        if acc is not None:
+            for dst, src in ((dk, acc[0]), (dv, acc[1])):
+                if hd > 0:
+                    dst[:, :, :hd].copy_(src[:, :hd].permute(0, 2, 1, 3))
+                if tl > 0:
+                    dst[:, :, Ls - tl:].copy_(src[:, hd:].permute(0, 2, 1, 3))
+        return dq, dk, dv, None, None, None, None, None, None, None
 
 
 def sequence_sharded_attention(q, k, v, mask: ChillMask, seq_len: int, sm_scale=None, group=None,
-                               local_forward=cabi_local_forward, local_backward=cabi_local_backward):
+                               local_forward=cabi_local_forward, local_backward=cabi_local_backward,
+                               halo_buffers=None):
     """Attention over a sequence split evenly across the ranks of ``group``.
 
     q, k, v: this rank's [B, H(_kv), L/N, D] shard (rank r holds positions [r*L/N, (r+1)*L/N));
-    ``seq_len`` is the global length L.  Differentiable; returns this rank's shard of O."""
+    ``seq_len`` is the global length L.  Differentiable; returns this rank's shard of O.
+
+    ``halo_buffers=(kbuf, vbuf)``: the HaloBuffers whose ``.local`` views are ``k`` and ``v``.  The neighbours'
+    halo rows are then received straight into the buffers' spare rows and K / V are never copied; the spare
+    rows must stay untouched until the backward pass has run.  Without it the call makes its own buffers and
+    copies k and v into them once."""
     if sm_scale is None:
         sm_scale = q.shape[-1] ** -0.5
-    return _SequenceShardedAttention.apply(q, k, v, mask, seq_len, sm_scale, group, local_forward, local_backward)
-
-
-# --------------------------------------------------------------------------- benchmark
-def bench_sequence_sharded(args, workload, metric):
-    """bench.py leg for the long sliding-window workload on N > 1 GPUs (already initialised NCCL)."""
-    from . import SlidingWindowChillMask
-
-    world, rank = dist.get_world_size(), dist.get_rank()
-    dev = torch.device("cuda", torch.cuda.current_device())
-    mname, margs, dt, B, H, L, D = workload
-    assert mname == "SlidingWindowChillMask" and L % world == 0
-    mask = SlidingWindowChillMask(*margs)
-    dtype = getattr(torch, dt)
-    Ls = L // world
-    g = torch.Generator(device=dev).manual_seed(20 + rank)
-    q, k, v, do = (torch.randn(B, H, Ls, D, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(4))
-    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
-
-    def step():
-        q.grad = k.grad = v.grad = None
-        o = sequence_sharded_attention(q, k, v, mask, L)
-        o.backward(do)
-
-    for _ in range(args.warmup):
-        step()
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    dist.barrier()
-    torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    pos = torch.arange(L, dtype=torch.int64)
-    lo, hi = type(mask).k_range_for_q(pos, L, mask.constargs)
-    pairs = int((hi - lo + 1).sum())
-    if rank == 0:
-        value = 14.0 * B * H * D * pairs / (ms.item() * 1e-3) / 1e12
-        halo = 2 * B * H * int(margs[0]) * D * q.element_size()
-        print(json.dumps({
-            "metric": metric, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms.item(), 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic: seeded N(0,1)",
-            "config": {"workload": f"c5: {mname}{margs} fwd+bwd {dt} (B={B},H={H},L={L},D={D}) sequence-sharded",
-                       "global_batch": B, "seq_len": L,
-                       "parallelism": f"sequence sharded over {world} GPUs, {halo} B K/V halo per boundary via NCCL send/recv, "
-                                      "dK/dV halo returned the same way"},
-            "gpu_launches": 4 * args.steps,
-        }), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
+    return _SequenceShardedAttention.apply(q, k, v, mask, seq_len, sm_scale, group, local_forward, local_backward,
+                                           halo_buffers)

@@ -117,6 +117,7 @@ bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int rows = imin(kTile, g.Lk - kb);
     zero_rows<T, D>(reinterpret_cast<T*>(p.dk) + b * p.dk_sb + hk * p.dk_sh + kb * p.dk_sl, p.dk_sl, rows, kFusedThreads);
     zero_rows<T, D>(reinterpret_cast<T*>(p.dv) + b * p.dv_sb + hk * p.dv_sh + kb * p.dv_sl, p.dv_sl, rows, kFusedThreads);
+    zero_part_rows<D>(p.part, b, hk, kb, rows, g.Lk, kFusedThreads);
     return;
   }
 
@@ -469,6 +470,7 @@ bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint8_t* stage = gen_base + L::kRing + wg * L::kTileBytes;
     const uint32_t tacc = wg == 0 ? tdV : tdK;
     const float mul = wg == 0 ? 1.f : g.scale;
+    float* part_row = p.part.row(wg == 0 ? p.part.dv : p.part.dk, b, hk, kb + r, g.Lk);
 #pragma unroll
     for (int q4 = 0; q4 < D / 32; ++q4) {
       uint32_t acc[32];
@@ -477,6 +479,7 @@ bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_wait_ld();
       }
       stage_row32<T>(stage, r, q4, acc, mul, ok && key_ok);
+      if (part_row != nullptr) store_part32(part_row + q4 * 32, acc, mul, ok && key_ok);
     }
     fence_proxy_async_smem();
     named_bar_sync(1, kBwdComputeThreads);
@@ -524,16 +527,11 @@ int launch_bwd_fused_one(const CUtensorMap* maps, const BwdTcParams& p, cudaStre
   auto kern = bwd_fused_tc_kernel<T, D, M>;
   constexpr int smem = FusedSmem<D>::kDynamic;
   static_assert(smem <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
-  static int configured_dev = -1;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured_dev = dev;
-  }
+  struct Tag {};
+  cudaError_t e = ensure_dynamic_smem<Tag>(kern, smem);
+  if (e != cudaSuccess) return (int)e;
   const Geo& g = p.g;
-  cudaError_t e = cudaMemsetAsync(p.dq_accum, 0, dq_accum_bytes(g.B, g.H, g.Lq, D), st);
+  e = cudaMemsetAsync(p.dq_accum, 0, dq_accum_bytes(g.B, g.H, g.Lq, D), st);
   if (e != cudaSuccess) return (int)e;
   // maps: 0 Q, 1 K, 2 V, 3 dO, 4 dQ, 5 dK, 6 dV
   dim3 gk((unsigned)(((g.Lk + kTile - 1) / kTile) * g.Hkv * g.B), 1, 1);

@@ -26,6 +26,7 @@
 #include "fwd_tc.cuh"
 #include "generic.cuh"
 #include "tc_common.cuh"
+#include "tc_launch.h"
 
 namespace chill {
 namespace tc {
@@ -45,6 +46,7 @@ struct BwdTcParams {
   int* status;
   int which;  // bit0: launch the dK/dV kernel, bit1: launch the dQ kernel
   float* dq_accum;  // fp32 accumulator of the single-kernel backward (bwd_fused.cuh), else nullptr
+  PartOut part;     // optional un-rounded fp32 copies of dK / dV rows
 };
 
 // fp32 dQ accumulator of the single-kernel backward (bwd_fused.cuh): one block of 128 rows x D channels per
@@ -103,6 +105,33 @@ __device__ __forceinline__ void stage_row32(uint8_t* tile, int r, int q4, const 
   }
 }
 
+// 32 un-rounded fp32 values (accumulator * mul, or zeros) of this thread's key row to the partial-output tensor.
+__device__ __forceinline__ void store_part32(float* dst, const uint32_t* acc, float mul, bool keep) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (keep)
+      v = make_float4(__uint_as_float(acc[4 * i]) * mul, __uint_as_float(acc[4 * i + 1]) * mul,
+                      __uint_as_float(acc[4 * i + 2]) * mul, __uint_as_float(acc[4 * i + 3]) * mul);
+    *reinterpret_cast<float4*>(dst + 4 * i) = v;
+  }
+}
+
+// Zero the partial-output rows that belong to key rows [kb, kb + rows) of (b, hk).
+template <int D>
+__device__ __forceinline__ void zero_part_rows(const PartOut& part, int b, int hk, int kb, int rows, int Lk, int nthreads) {
+  if (part.dk == nullptr) return;
+  for (int idx = threadIdx.x; idx < rows * (D / 4); idx += nthreads) {
+    const int r = idx / (D / 4), c = idx % (D / 4);
+    float* a = part.row(part.dk, b, hk, kb + r, Lk);
+    float* bb = part.row(part.dv, b, hk, kb + r, Lk);
+    if (a != nullptr) {
+      *reinterpret_cast<float4*>(a + 4 * c) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(bb + 4 * c) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+}
+
 // =========================================================================== dK / dV
 // TMEM: S^T (128 columns, overlaid by the 16-bit P^T), dP^T (128, overlaid by dS^T), dV, dK: 512 columns,
 // every MMA at N = 128.  Tensor-core order in steady state (u = query tile):
@@ -152,6 +181,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int rows = imin(kTile, g.Lk - kb);
     zero_rows<T, D>(reinterpret_cast<T*>(p.dk) + b * p.dk_sb + hk * p.dk_sh + kb * p.dk_sl, p.dk_sl, rows, kBwdThreads);
     zero_rows<T, D>(reinterpret_cast<T*>(p.dv) + b * p.dv_sb + hk * p.dv_sh + kb * p.dv_sl, p.dv_sl, rows, kBwdThreads);
+    zero_part_rows<D>(p.part, b, hk, kb, rows, g.Lk, kBwdThreads);
     return;
   }
 
@@ -414,6 +444,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* stage = gen_base + L::kRing + wg * L::kTileBytes;
     const uint32_t tacc = wg == 0 ? tdV : tdK;
     const float mul = wg == 0 ? 1.f : g.scale;
+    float* part_row = p.part.row(wg == 0 ? p.part.dv : p.part.dk, b, hk, kb + r, g.Lk);
 #pragma unroll
     for (int q4 = 0; q4 < D / 32; ++q4) {
       uint32_t acc[32];
@@ -422,6 +453,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_wait_ld();
       }
       stage_row32<T>(stage, r, q4, acc, mul, ok && key_ok);
+      if (part_row != nullptr) store_part32(part_row + q4 * 32, acc, mul, ok && key_ok);
     }
     fence_proxy_async_smem();
     named_bar_sync(1, kBwdComputeThreads);
@@ -761,16 +793,12 @@ int launch_bwd_one(const CUtensorMap* maps, const BwdTcParams& p, cudaStream_t s
   constexpr int smem = BwdSmem<D>::kDynamic;
   constexpr int smem_dq = DqSmem<D>::kDynamic;
   static_assert(smem_dq <= 232448 && smem <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
-  static int configured_dev = -1;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq);
-    if (e != cudaSuccess) return (int)e;
-    configured_dev = dev;
-  }
+  struct TagDkdv {};
+  struct TagDq {};
+  cudaError_t ea = ensure_dynamic_smem<TagDkdv>(kdkdv, smem);
+  if (ea != cudaSuccess) return (int)ea;
+  ea = ensure_dynamic_smem<TagDq>(kdq, smem_dq);
+  if (ea != cudaSuccess) return (int)ea;
   const Geo& g = p.g;
   // maps: 0 Q, 1 K, 2 V, 3 dO, 4 dQ, 5 dK, 6 dV
   if (p.which & 1) {

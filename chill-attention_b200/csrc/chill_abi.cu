@@ -5,6 +5,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "bwd_tc.cuh"
@@ -17,6 +18,7 @@ namespace chill {
 
 static thread_local char g_cuda_err[256] = "";
 __device__ int g_device_status = 0;
+static std::atomic<unsigned long long> g_launches{0};  // kernels launched by this library (chill_launch_count)
 
 static int cuda_fail(cudaError_t e, const char* what) {
   snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
@@ -52,11 +54,25 @@ static int check_shape(const chill_shape& s) {
   return CHILL_OK;
 }
 
-static MaskArgs to_mask_args(const chill_mask_desc& m) {
+// The functors do their index arithmetic in 32 bits (position + constant), so the 64-bit constants of the ABI are
+// saturated first.  For the built-in masks every constant is a distance or a size measured in positions, and any value
+// beyond +-seq_len selects the same pairs as +-seq_len itself, so they are clamped there ("unbounded" written as
+// 2**31 - 1 or 2**40 stays unbounded).  Constants of a custom functor are saturated to +-2^30, which still leaves
+// room for adding a position.
+static MaskArgs to_mask_args(const chill_mask_desc& m, long long seq_len) {
   MaskArgs a;
+  const long long lim = (m.id >= 0 && m.id < CHILL_MASK_CUSTOM && seq_len > 0) ? seq_len : (1ll << 30);
   for (int i = 0; i < 8; ++i) {
-    a.i[i] = i < m.n_args ? (int)m.i[i] : 0;
+    long long v = i < m.n_args ? (long long)m.i[i] : 0;
+    v = v > lim ? lim : (v < -lim ? -lim : v);
+    a.i[i] = (int)v;
     a.f[i] = i < m.n_args ? (float)m.f[i] : 0.f;
+  }
+  if (m.id == CHILL_MASK_CHUNKWISE && a.i[0] > 0 && seq_len > 0) {
+    // back_contexts counts chunks: more chunks than the sequence has changes nothing, and (chunk + back + 1) * size
+    // then stays far below 2^31
+    const int n_chunks = (int)((seq_len + a.i[0] - 1) / a.i[0]);
+    a.i[1] = a.i[1] > n_chunks ? n_chunks : (a.i[1] < -n_chunks ? -n_chunks : a.i[1]);
   }
   return a;
 }
@@ -65,7 +81,7 @@ static Geo to_geo(const chill_shape& s) {
   Geo g;
   g.B = s.B; g.H = s.H; g.Hkv = s.H_kv; g.Lq = s.Lq; g.Lk = s.Lk; g.D = s.D;
   g.q_off = s.q_offset; g.k_off = s.k_offset; g.seq_len = s.seq_len;
-  g.scale = s.sm_scale; g.lens = s.lens; g.margs = to_mask_args(s.mask);
+  g.scale = s.sm_scale; g.lens = s.lens; g.margs = to_mask_args(s.mask, s.seq_len);
   return g;
 }
 
@@ -200,6 +216,7 @@ static int fwd_generic(const chill_fwd_args& a, cudaStream_t st) {
   CHILL_MASK_SWITCH(a.s.mask.id,
                     CHILL_DTYPE_SWITCH(a.s.dtype, (fwd_generic_kernel<ElemT, MaskT><<<grid, kGenericWarps * 32, 0, st>>>(p))))
   cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) g_launches += 1;
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "fwd_generic launch");
 }
 
@@ -230,6 +247,7 @@ static int fwd_tc(const chill_fwd_args& a, cudaStream_t st) {
   } else {
     CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_fwd<MaskT>(s.dtype, s.D, maps, p, grid, st)))
   }
+  if (e == 0) g_launches += 1;
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "fwd_tc launch");
 }
 
@@ -240,6 +258,14 @@ static int check_bwd(const chill_bwd_args* a, bool need_all) {
   if (st != CHILL_OK) return st;
   if (!a->o || !a->d_o || !a->delta) return CHILL_E_INVALID;
   if (need_all && (!a->q || !a->k || !a->v || !a->lse || !a->dq || !a->dk || !a->dv)) return CHILL_E_INVALID;
+  if ((a->dk_part == nullptr) != (a->dv_part == nullptr)) return CHILL_E_INVALID;
+  if (a->dk_part != nullptr) {
+    if (a->part_head < 0 || a->part_tail < 0 || (long long)a->part_head + a->part_tail > a->s.Lk) return CHILL_E_INVALID;
+    // rows are written 16 bytes at a time
+    if (((uintptr_t)a->dk_part | (uintptr_t)a->dv_part) % 16 != 0 || a->s.D % 4 != 0) return CHILL_E_INVALID;
+    for (int i = 0; i < 3; ++i)
+      if (a->part_strides[i] % 4 != 0 || a->part_strides[i] < 0) return CHILL_E_INVALID;
+  }
   return CHILL_OK;
 }
 
@@ -254,6 +280,16 @@ static bool bwd_tc_eligible(const chill_bwd_args& a) {
          tma_ok(a.dv, a.dv_strides, s.B, s.H_kv, s.Lk, es) && a.lse_strides[2] == 1;
 }
 
+static PartOut to_part(const chill_bwd_args& a) {
+  PartOut o;
+  if (a.dk_part != nullptr && a.dv_part != nullptr && a.part_head + a.part_tail > 0) {
+    o.dk = a.dk_part; o.dv = a.dv_part;
+    o.sb = a.part_strides[0]; o.sh = a.part_strides[1]; o.sl = a.part_strides[2];
+    o.head = a.part_head; o.tail = a.part_tail;
+  }
+  return o;
+}
+
 static BwdP to_bwdp(const chill_bwd_args& a) {
   BwdP p;
   p.g = to_geo(a.s);
@@ -263,6 +299,7 @@ static BwdP to_bwdp(const chill_bwd_args& a) {
   p.lse = a.lse;
   p.lse_sb = a.lse_strides[0]; p.lse_sh = a.lse_strides[1]; p.lse_sl = a.lse_strides[2];
   p.delta = a.delta;
+  p.part = to_part(a);
   return p;
 }
 
@@ -291,6 +328,7 @@ static int delta_launch(const chill_bwd_args& a, cudaStream_t st) {
     CHILL_DTYPE_SWITCH(s.dtype, (delta_kernel<ElemT><<<grid, kGenericWarps * 32, 0, st>>>(o, d_o, a.delta, s.H, s.Lq, s.D, a.d_lse, dl[0], dl[1], dl[2])))
   }
   cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) g_launches += 1;
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "delta launch");
 }
 
@@ -311,6 +349,7 @@ static int bwd_generic(const chill_bwd_args& a, cudaStream_t st) {
                       if (which & 1) (bwd_dkdv_generic_kernel<ElemT, MaskT><<<gk, kGenericWarps * 32, 0, st>>>(p));
                     }))
   cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) g_launches += (which == 3 ? 2 : 1);
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "bwd_generic launch");
 }
 
@@ -319,6 +358,7 @@ static int bwd_generic(const chill_bwd_args& a, cudaStream_t st) {
 struct SideStream {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
+  std::mutex mu;  // held across one fork / launch / join sequence
 };
 
 static SideStream* side_stream() {
@@ -364,16 +404,21 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = tr
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
   p.which = bwd_which(s.flags);
   p.dq_accum = nullptr;
+  p.part = to_part(a);
   int e = 0;
   if (fused && p.which == 3 && a.dq_accum != nullptr) {
     if ((reinterpret_cast<uintptr_t>(a.dq_accum) & 15u) != 0) return CHILL_E_INVALID;
     p.dq_accum = a.dq_accum;  // single-kernel backward + conversion of the fp32 dQ sums
     CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd<MaskT>(s.dtype, s.D, maps, p, st)))
+    if (e == 0) g_launches += 2;
     return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_fused launch");
   }
   SideStream* side = (concurrent && p.which == 3) ? side_stream() : nullptr;
   if (side != nullptr) {
-    // fork: dK/dV on the caller's stream, dQ on the side stream; join back before returning
+    // fork: dK/dV on the caller's stream, dQ on the side stream; join back before returning.  The helper stream and
+    // its two events are shared by every caller on this device, so the whole record / wait / launch / record / wait
+    // sequence is one critical section: a second host thread must not re-record `fork` or `join` in between.
+    std::lock_guard<std::mutex> lock(side->mu);
     cudaError_t ce = cudaEventRecord(side->fork, st);
     if (ce == cudaSuccess) ce = cudaStreamWaitEvent(side->stream, side->fork, 0);
     if (ce != cudaSuccess) return cuda_fail(ce, "bwd fork");
@@ -386,9 +431,11 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = tr
     ce = cudaEventRecord(side->join, side->stream);
     if (ce == cudaSuccess) ce = cudaStreamWaitEvent(st, side->join, 0);
     if (ce != cudaSuccess) return cuda_fail(ce, "bwd join");
+    if (e == 0) g_launches += 2;
     return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tc launch");
   }
   CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd<MaskT>(s.dtype, s.D, maps, p, st)))
+  if (e == 0) g_launches += (p.which == 3 ? 2 : 1);
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tc launch");
 }
 
@@ -515,13 +562,14 @@ int chill_bwd_noalloc(const chill_bwd_args* a, void* stream) {
 int chill_mask_tabulate(const chill_mask_desc* m, int32_t n, int32_t tile, uint8_t* dense, int32_t* k_lims,
                         int32_t* q_lims, int32_t* k_full, int32_t* q_full, void* stream) {
   if (m == nullptr || n <= 0 || tile <= 0 || n > 32768) return CHILL_E_INVALID;
-  MaskArgs a = to_mask_args(*m);
+  MaskArgs a = to_mask_args(*m, n);
   const long long total = dense != nullptr ? (long long)n * n : (long long)n;
   const int threads = 256;
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   cudaStream_t st = (cudaStream_t)stream;
   CHILL_MASK_SWITCH(m->id, (mask_tabulate_kernel<MaskT><<<blocks, threads, 0, st>>>(a, n, tile, dense, k_lims, q_lims, k_full, q_full)))
   cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) g_launches += 1;
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "mask_tabulate launch");
 }
 
@@ -529,6 +577,8 @@ int chill_mask_traits(int32_t mask_id) {
   CHILL_MASK_SWITCH(mask_id, return traits_of<MaskT>())
   return CHILL_E_UNSUPPORTED;
 }
+
+unsigned long long chill_launch_count(void) { return g_launches.load(); }
 
 int chill_read_device_status(void) {
   int* p = device_status_ptr();

@@ -38,12 +38,30 @@ struct FwdP {
   long long lse_sb, lse_sh, lse_sl;
 };
 
+// Optional fp32 copies of the un-rounded dK (times sm_scale) and dV for the first `head` and the last `tail` key
+// rows of a call: key row j < head is part row j, key row j >= Lk - tail is part row head + j - (Lk - tail).
+struct PartOut {
+  float *dk = nullptr, *dv = nullptr;
+  long long sb = 0, sh = 0, sl = 0;  // element strides of [batch][kv head][part row]; channels are contiguous
+  int head = 0, tail = 0;
+  // address of the part row of key row j in tensor `t` (dk or dv), or nullptr if the row is outside both windows
+  __device__ __forceinline__ float* row(float* t, int b, int hk, int j, int Lk) const {
+    if (t == nullptr || j >= Lk) return nullptr;
+    int pr;
+    if (j < head) pr = j;
+    else if (j >= Lk - tail) pr = head + j - (Lk - tail);
+    else return nullptr;
+    return t + b * sb + hk * sh + pr * sl;
+  }
+};
+
 struct BwdP {
   Geo g;
   TRef q, k, v, o, d_o, dq, dk, dv;
   const float* lse;
   long long lse_sb, lse_sh, lse_sl;
   float* delta;  // contiguous [B][H][Lq]
+  PartOut part;
 };
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -298,10 +316,13 @@ __global__ void __launch_bounds__(kGenericWarps * 32) bwd_dkdv_generic_kernel(Bw
   const int D = g.D;
   T* dkrow = row_ptr_w<T>(p.dk, b, hk, j);
   T* dvrow = row_ptr_w<T>(p.dv, b, hk, j);
+  float* dkpart = p.part.row(p.part.dk, b, hk, j, g.Lk);
+  float* dvpart = p.part.row(p.part.dv, b, hk, j, g.Lk);
   if (kg >= n) {
     for (int d = lane; d < D; d += 32) {
       dkrow[d * p.dk.sd] = from_f<T>(0.f);
       dvrow[d * p.dv.sd] = from_f<T>(0.f);
+      if (dkpart != nullptr) dkpart[d] = dvpart[d] = 0.f;
     }
     return;
   }
@@ -360,6 +381,10 @@ __global__ void __launch_bounds__(kGenericWarps * 32) bwd_dkdv_generic_kernel(Bw
     if (d < D) {
       dkrow[d * p.dk.sd] = from_f<T>(acck[t] * g.scale);
       dvrow[d * p.dv.sd] = from_f<T>(accv[t]);
+      if (dkpart != nullptr) {
+        dkpart[d] = acck[t] * g.scale;
+        dvpart[d] = accv[t];
+      }
     }
   }
 }

@@ -5,6 +5,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "generic.cuh"
 
 namespace chill {
@@ -12,6 +14,28 @@ namespace tc {
 struct FwdTcParams;
 struct BwdTcParams;
 }  // namespace tc
+
+// Raises a kernel's dynamic shared-memory limit the first time the kernel is launched on a device.  The attribute
+// is per (kernel, device); the record of where it has been set is per call site (pass a distinct `Tag` per kernel)
+// and guarded by a mutex, so host threads driving different devices do not race on it.
+template <class Tag, class Kern>
+inline cudaError_t ensure_dynamic_smem(Kern kern, int smem_bytes, bool prefer_max_carveout = false) {
+  constexpr int kMaxDevices = 64;
+  static bool done[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return e;
+  if (prefer_max_carveout)
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  done[dev] = true;
+  return cudaSuccess;
+}
 
 // maps: Q, K, V, O.  Returns a cudaError_t cast to int.
 template <class M>

@@ -2,12 +2,18 @@
  * chill_b200.h - C ABI of the B200 (sm_100a) masked flash-attention kernels.
  *
  * Every entry point takes plain device pointers, element strides and sizes; none
- * allocates device memory, synchronises, or keeps state between calls, apart from a
- * per-process cache of the driver entry point used to encode TMA descriptors and,
- * for chill_bwd, one helper stream + two events per device (created on the first
- * call) on which the dQ kernel runs beside the dK/dV kernel; chill_bwd joins that
- * stream back into the caller's stream before it returns, so stream ordering as
- * seen by the caller is unchanged.
+ * allocates device memory, synchronises, or keeps state between calls, apart from:
+ *  - a per-process cache of the driver entry point used to encode TMA descriptors and
+ *    a per-device record of which kernels had their shared-memory limit raised;
+ *  - for the two-kernel form of chill_bwd, one helper stream + two events per device
+ *    (created on the first call) on which the dQ kernel runs beside the dK/dV kernel;
+ *    chill_bwd joins that stream back into the caller's stream before it returns, so
+ *    stream ordering as seen by the caller is unchanged.  The fork / launch / join
+ *    sequence holds a per-device lock, so host threads may call chill_bwd on the same
+ *    device from different streams;
+ *  - for chill_bwd_noalloc, a 16 MiB array in device global memory per GPU (part of
+ *    the library image) and a per-device cache of its address;
+ *  - a process-wide count of launched kernels (chill_launch_count).
  * All work is enqueued on the CUDA stream passed in (a cudaStream_t cast to
  * void*; NULL = the default stream) of the CURRENT device.  Return value: 0 on
  * success, a negative CHILL_E_* code otherwise; nothing aborts the process.
@@ -39,7 +45,7 @@
 extern "C" {
 #endif
 
-#define CHILL_ABI_VERSION 3
+#define CHILL_ABI_VERSION 4
 
 /* status codes */
 #define CHILL_OK 0
@@ -140,6 +146,16 @@ typedef struct chill_bwd_args {
    * with NULL the behaviour is the reference's. */
   const float* d_lse;
   int64_t dlse_strides[3];
+  /* Optional (may be NULL, both or neither): un-rounded fp32 copies of dK (already multiplied by sm_scale) and dV
+   * for the first `part_head` and the last `part_tail` key rows of the call (part_head + part_tail <= Lk).  Key row
+   * j < part_head goes to part row j, key row j >= Lk - part_tail to part row part_head + j - (Lk - part_tail);
+   * element (b, h_kv, part row, channel) sits at b * part_strides[0] + h_kv * part_strides[1] + row * part_strides[2]
+   * + channel.  The 16-bit dk / dv are written as usual.  For callers that add several partial dK / dV of the same
+   * key rows (a sequence-sharded backward sums the contribution of its own queries and of a neighbour's) and
+   * want to round once, after the sum.  No counterpart in the reference, which is single-device. */
+  float *dk_part, *dv_part;
+  int64_t part_strides[3];
+  int32_t part_head, part_tail;
 } chill_bwd_args;
 
 /* O = softmax(mask(Q K^T * sm_scale)) V and LSE.  See chill_shape for conventions. */
@@ -209,6 +225,10 @@ int chill_mask_traits(int32_t mask_id);
 /* Device-side error word.  Kernels with bounded waits record a non-zero code here instead
  * of hanging; reading it synchronises the device. Returns the code (0 = none) and clears it. */
 int chill_read_device_status(void);
+
+/* Number of kernels this library has launched in the calling process so far (all devices, all streams;
+ * memsets and copies are not counted).  A benchmark reads it before and after a timed region. */
+unsigned long long chill_launch_count(void);
 
 int chill_abi_version(void);
 const char* chill_status_string(int status);

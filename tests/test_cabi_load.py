@@ -39,11 +39,12 @@ def test_struct_sizes_match_header(lib):
     assert ctypes.sizeof(_cabi.MaskDesc) == 8 + 64 + 64
     assert ctypes.sizeof(_cabi.Shape) == 56 + 136
     assert ctypes.sizeof(_cabi.FwdArgs) == 192 + 5 * 8 + 4 * 32 + 24
-    assert ctypes.sizeof(_cabi.BwdArgs) == 192 + 10 * 8 + 8 * 32 + 24 + 8 + 8 + 24  # last: dq_accum, d_lse + strides
+    assert ctypes.sizeof(_cabi.BwdArgs) == 192 + 10 * 8 + 8 * 32 + 24 + 8 + 8 + 24 + 16 + 24 + 8
+    # last: dq_accum, d_lse + strides, dk_part / dv_part, part_strides, part_head / part_tail
 
 
 def test_host_only_entry_points(lib):
-    assert lib.chill_abi_version() == 3
+    assert lib.chill_abi_version() == 4
     assert lib.chill_status_string(0) == b"ok"
     assert b"invalid" in lib.chill_status_string(-1)
     # bit0 k full range, bit1 q full range, bit2/3 continuous limits, bit4 guaranteed safe

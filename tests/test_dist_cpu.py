@@ -14,26 +14,37 @@ import torch.multiprocessing as mp
 from helpers import ROOT
 
 
-def _oracle_local_forward(mask, q, k_ext, v_ext, q_off, k_off, seq_len, sm_scale):
+def _oracle_local_forward(mask, q, k_ext, v_ext, q_off, k_off, seq_len, sm_scale, o, lse):
     from oracle import attention_oracle as orc
 
     qp = torch.arange(q_off, q_off + q.shape[2])
     kp = torch.arange(k_off, k_off + k_ext.shape[2])
     md = orc.builtin_mask_dense(mask.name, mask.constargs, qp, kp)
-    o, lse = orc.attention_forward(md, q, k_ext, v_ext, None, sm_scale, torch.float64, qp, kp, seq_len)
-    return o, lse
+    o_ref, lse_ref = orc.attention_forward(md, q, k_ext, v_ext, None, sm_scale, torch.float64, qp, kp, seq_len)
+    o.copy_(o_ref)
+    lse.copy_(lse_ref)
 
 
-def _oracle_local_backward(mask, q, k_ext, v_ext, o, lse, do, q_off, k_off, seq_len, sm_scale):
+def _oracle_local_backward(mask, q, k_ext, v_ext, o, lse, do, q_off, k_off, seq_len, sm_scale, dq, dk, dv, part):
     from oracle import attention_oracle as orc
 
     qp = torch.arange(q_off, q_off + q.shape[2])
     kp = torch.arange(k_off, k_off + k_ext.shape[2])
     md = orc.builtin_mask_dense(mask.name, mask.constargs, qp, kp)
-    return orc.attention_backward(md, q, k_ext, v_ext, do, None, sm_scale, torch.float64, qp, kp, seq_len)
+    rdq, rdk, rdv = orc.attention_backward(md, q, k_ext, v_ext, do, None, sm_scale, torch.float64, qp, kp, seq_len)
+    dq.copy_(rdq)
+    # the 16-bit results of a real kernel are rounded; mimic that here so that a wrong use of them shows
+    dk.copy_(rdk.to(torch.bfloat16))
+    dv.copy_(rdv.to(torch.bfloat16))
+    if part is not None:
+        dkp, dvp, head, tail = part
+        Lk = k_ext.shape[2]
+        for dst, src in ((dkp, rdk), (dvp, rdv)):
+            dst[:, :, :head] = src[:, :, :head]
+            dst[:, :, head:head + tail] = src[:, :, Lk - tail:]
 
 
-def _worker(rank, world, port, mask_name, mask_args, L, fail_rank):
+def _worker(rank, world, port, mask_name, mask_args, L, fail_rank, use_buffers=False):
     for p in (os.path.join(ROOT, "chill-attention_b200"), ROOT, os.path.join(ROOT, "tests")):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -56,8 +67,20 @@ def _worker(rank, world, port, mask_name, mask_args, L, fail_rank):
             with pytest.raises(ValueError):
                 cdist.halo_sizes(mask, Ls)
             return
-        ql, kl, vl = (t[:, :, sl].clone().requires_grad_(True) for t in (q, k, v))
-        o = cdist.sequence_sharded_attention(ql, kl, vl, mask, L, group=None,
+        left, right = cdist.halo_sizes(mask, Ls)
+        ql = q[:, :, sl].clone().requires_grad_(True)
+        if use_buffers:
+            # K and V live in HaloBuffers: the halo rows are received straight into their spare rows
+            kbuf = cdist.HaloBuffer(B, Hkv, Ls, D, left, right, torch.float64, "cpu")
+            vbuf = cdist.HaloBuffer(B, Hkv, Ls, D, left, right, torch.float64, "cpu")
+            kbuf.storage.fill_(float("nan")), vbuf.storage.fill_(float("nan"))  # unreceived rows must never be read
+            kbuf.local.copy_(k[:, :, sl]), vbuf.local.copy_(v[:, :, sl])
+            kl, vl = kbuf.local.requires_grad_(True), vbuf.local.requires_grad_(True)
+            buffers = (kbuf, vbuf)
+        else:
+            kl, vl = (t[:, :, sl].clone().requires_grad_(True) for t in (k, v))
+            buffers = None
+        o = cdist.sequence_sharded_attention(ql, kl, vl, mask, L, group=None, halo_buffers=buffers,
                                              local_forward=_oracle_local_forward, local_backward=_oracle_local_backward)
         o.backward(do[:, :, sl])
         pos = torch.arange(L)
@@ -66,8 +89,17 @@ def _worker(rank, world, port, mask_name, mask_args, L, fail_rank):
         dq, dk, dv = orc.attention_backward(md, q, k, v, do)
         torch.testing.assert_close(o.detach(), o_ref[:, :, sl], atol=1e-10, rtol=1e-10)
         torch.testing.assert_close(ql.grad, dq[:, :, sl], atol=1e-10, rtol=1e-10)
-        torch.testing.assert_close(kl.grad, dk[:, :, sl], atol=1e-10, rtol=1e-10)
-        torch.testing.assert_close(vl.grad, dv[:, :, sl], atol=1e-10, rtol=1e-10)
+        # Key rows that receive contributions from more than one call (this rank's boundary + interior calls, a
+        # neighbour's boundary call) must be summed before any rounding: exact here.  The rows in between come
+        # from the interior call's 16-bit output alone, which the stand-in kernel above rounds to bf16.
+        must_be_exact = torch.zeros(Ls, dtype=torch.bool)
+        if rank > 0:
+            must_be_exact[:min(Ls, left + right)] = True
+        if rank < world - 1:
+            must_be_exact[max(0, Ls - left - right):] = True
+        for mine, ref in ((kl.grad, dk[:, :, sl]), (vl.grad, dv[:, :, sl])):
+            torch.testing.assert_close(mine[:, :, must_be_exact], ref[:, :, must_be_exact], atol=1e-10, rtol=1e-10)
+            torch.testing.assert_close(mine, ref, atol=2e-2, rtol=1e-2)
     finally:
         dist.destroy_process_group()
 
@@ -81,8 +113,9 @@ def _spawn(world, *a):
 @pytest.mark.parametrize("mask", [("SlidingWindowChillMask", (10, 0)), ("SlidingWindowChillMask", (7, 5)),
                                   ("SlidingWindowChillMask", (9, 8)),  # both boundaries overlap on a 16-row shard
                                   ("ChunkwiseChillMask", (6, 1))], ids=str)
-def test_sequence_sharded_equals_single_process(world, mask):
-    _spawn(world, mask[0], mask[1], 48, None)
+@pytest.mark.parametrize("use_buffers", [False, True], ids=["copied", "halo_buffers"])
+def test_sequence_sharded_equals_single_process(world, mask, use_buffers):
+    _spawn(world, mask[0], mask[1], 48, None, use_buffers)
 
 
 def test_window_wider_than_shard_is_refused():

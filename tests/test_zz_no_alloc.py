@@ -16,7 +16,7 @@ import ctypes
 import pytest
 import torch
 
-from helpers import G_RTOL, ensure_built, make_inputs
+from helpers import G_RTOL, check_grads, ensure_built, make_inputs, oracle_all
 
 pytestmark = pytest.mark.gpu
 
@@ -74,6 +74,52 @@ def test_noalloc_matches_regular_backward_twice_in_a_row():
     out3, _ = _both_paths(lib, p1)
     for a, b in zip(out3, out1):
         assert torch.equal(a, b)
+    assert lib.chill_read_device_status() == 0
+    # not only equal to the regular path: right, against the fp64 dense-mask oracle
+    for prob, out, mask, dtype, ln in ((p1, out1, ca.CausalChillMask(), torch.bfloat16, None),
+                                       (p2, out2, ca.SlidingWindowChillMask(40, 3), torch.float32, lens)):
+        q, k, v, do = (t.cpu() for t in prob[:4])
+        check_grads(out, oracle_all(mask, q, k, v, do, ln)[2:], dtype, ln)
+
+
+def test_noalloc_allocates_nothing_and_honours_flags_and_dlse():
+    """After the one-time address look-up of the first call on the device, a call must leave both the driver's
+    free-memory figure and torch's allocator untouched; CHILL_FLAG_REQUIRE_TC and the optional d_lse input behave
+    as in chill_bwd."""
+    import chill_attention as ca
+    from chill_attention import _cabi
+
+    ensure_built()
+    lib = _cabi.load_library()
+    mask = ca.CausalChillMask()
+    q, k, v, do, o, lse, shape, _ = _problem(lib, mask, 1, 4, 4, 512, 128, torch.bfloat16, seed=8)
+    out = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    _cabi.backward_noalloc(lib, q, k, v, o, do, lse, *out, shape)  # first call: resolves the array's address
+    torch.cuda.synchronize()
+    a = _cabi.backward_args(q, k, v, o, do, lse, None, *out, shape)
+    free0, alloc0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(3):
+        _cabi.check(lib, lib.chill_bwd_noalloc(ctypes.byref(a), _cabi._stream()), "chill_bwd_noalloc")
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert torch.cuda.memory_allocated() == alloc0 and torch.cuda.memory_reserved() == reserved0
+    # REQUIRE_TC: served by the tensor-core kernels here, refused for a shape only the generic kernels take
+    shape_tc = _cabi.make_shape(q, k, _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor], (), None, 128 ** -0.5, flags=_cabi.FLAG_REQUIRE_TC)
+    _cabi.backward_noalloc(lib, q, k, v, o, do, lse, *out, shape_tc)
+    q32 = q.float()
+    shape32 = _cabi.make_shape(q32, q32, _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor], (), None, 128 ** -0.5, flags=_cabi.FLAG_REQUIRE_TC)
+    a32 = _cabi.backward_args(q32, q32, q32, q32, q32, lse, None, q32.clone(), q32.clone(), q32.clone(), shape32)
+    assert lib.chill_bwd_noalloc(ctypes.byref(a32), _cabi._stream()) == -2
+    # d_lse is folded into delta exactly as by chill_bwd_delta
+    d_lse = torch.randn(lse.shape, device="cuda", dtype=torch.float32)
+    ref = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    delta = torch.empty_like(lse)
+    _cabi.backward(lib, q, k, v, o, do, lse, delta, *ref, shape, deterministic=True, d_lse=d_lse)
+    ad = _cabi.backward_args(q, k, v, o, do, lse, None, *out, shape, d_lse=d_lse)
+    _cabi.check(lib, lib.chill_bwd_noalloc(ctypes.byref(ad), _cabi._stream()), "chill_bwd_noalloc")
+    torch.cuda.synchronize()
+    for x, y in zip(out, ref):
+        assert torch.equal(x, y)  # both ran the two-kernel backward on the same delta
     assert lib.chill_read_device_status() == 0
 
 
