@@ -39,7 +39,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 // Upper bound (ns) the hardware may keep the thread suspended inside one try_wait; a waiter wakes
 // as soon as the phase completes, so a generous hint only cuts down on polling instructions that
 // would otherwise compete for issue slots with the warps doing the math.
-constexpr uint32_t kSuspendHintNs = 200000u;
+#ifndef CHILL_SUSPEND_HINT_NS
+#define CHILL_SUSPEND_HINT_NS 200000u
+#endif
+constexpr uint32_t kSuspendHintNs = CHILL_SUSPEND_HINT_NS;
 
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;

@@ -25,9 +25,6 @@ static int launch_fwd_one(const CUtensorMap* maps, const tc::FwdTcParams& p, dim
   return (int)cudaGetLastError();
 }
 
-}  // namespace chill
-
-namespace chill {
 template <>
 int tc_launch_fwd<InstMask>(int dtype, int D, const CUtensorMap* maps, const tc::FwdTcParams& p, dim3 grid,
                             cudaStream_t st) {
