@@ -33,11 +33,13 @@ BUILTIN_FUNCTOR_IDS = {
 _DTYPES = {torch.float32: CHILL_F32, torch.float16: CHILL_F16, torch.bfloat16: CHILL_BF16}
 
 ABI_VERSION = 4
+SELFTEST_STATUS = 901
 
 EXPORTS = (
     "chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_bwd_scratch_bytes", "chill_bwd_dq_accum_bytes",
     "chill_fwd_uses_tensor_cores",
-    "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits", "chill_read_device_status",
+    "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_tabulate_blocks", "chill_mask_traits",
+    "chill_read_device_status", "chill_selftest_bounded_wait",
     "chill_launch_count", "chill_abi_version", "chill_status_string", "chill_last_cuda_error",
 )
 
@@ -106,13 +108,16 @@ def load_library(path: str | None = None) -> C.CDLL:
         lib.chill_fwd_uses_tensor_cores.argtypes = [C.POINTER(FwdArgs)]
         lib.chill_bwd_uses_tensor_cores.argtypes = [C.POINTER(BwdArgs)]
         lib.chill_mask_tabulate.argtypes = [C.POINTER(MaskDesc), C.c_int32, C.c_int32] + [C.c_void_p] * 6
+        lib.chill_mask_tabulate_blocks.argtypes = [C.POINTER(MaskDesc), C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+        lib.chill_selftest_bounded_wait.argtypes = [C.c_int32, C.c_void_p]
         lib.chill_mask_traits.argtypes = [C.c_int32]
         lib.chill_status_string.argtypes = [C.c_int]
         lib.chill_status_string.restype = C.c_char_p
         lib.chill_last_cuda_error.restype = C.c_char_p
         lib.chill_launch_count.restype = C.c_ulonglong
         for name in ("chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_fwd_uses_tensor_cores",
-                     "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_traits",
+                     "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_tabulate_blocks", "chill_mask_traits",
+                     "chill_selftest_bounded_wait",
                      "chill_read_device_status", "chill_abi_version"):
             getattr(lib, name).restype = C.c_int
         if lib.chill_abi_version() != ABI_VERSION:

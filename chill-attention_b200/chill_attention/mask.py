@@ -194,7 +194,49 @@ class ChillMask:
         """FlexAttention ``mask_mod(b, h, q_idx, kv_idx)`` callable or None."""
         return None
 
-    def verify(self, max_pos):
+    def device_tables(self, max_pos, tile, block_tiles=()):
+        """Tabulate this mask's CUDA functor on the GPU (the functions the kernels are compiled with, in the library
+        ``register_chill_mask`` would use, built on demand for a custom header).  Returns CPU tensors
+        ``dense`` bool (n, n), ``k_lims`` / ``q_lims`` int (n, 2), ``k_full`` / ``q_full`` int (ceil(n / tile), 2),
+        ``blocks`` {(q_tile, k_tile): bool (n_q_tiles, n_k_tiles)} for the pairs in ``block_tiles`` and ``traits``
+        (bit0 has_k_full_range, bit1 has_q_full_range, bit2 k_lims_continious, bit3 q_lims_continious, bit4
+        is_guaranteed_safe).  Counterpart of the reference's _mask_infer / _limits_infer / _full_ranges_infer
+        (mask.py:284-377, :487-534)."""
+        import ctypes
+
+        from . import _cabi
+        from .chill import _resolve_functor
+
+        lib, functor_id = _resolve_functor(self)
+        n = int(max_pos)
+        if not torch.cuda.is_available():
+            raise RuntimeError("device tables need a CUDA device")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        nt = (n + tile - 1) // tile
+        dense = torch.empty(n * n, dtype=torch.uint8, device=dev)
+        k_lims, q_lims = (torch.empty(n, 2, dtype=torch.int32, device=dev) for _ in range(2))
+        k_full, q_full = (torch.empty(nt, 2, dtype=torch.int32, device=dev) for _ in range(2))
+        desc = _cabi.mask_desc(functor_id, self.constargs)
+        with torch.cuda.device(dev):
+            st = _cabi._stream()
+            _cabi.check(lib, lib.chill_mask_tabulate(ctypes.byref(desc), n, tile, dense.data_ptr(), k_lims.data_ptr(),
+                                                      q_lims.data_ptr(), k_full.data_ptr(), q_full.data_ptr(), st),
+                        "chill_mask_tabulate")
+            blocks = {}
+            for qt, kt in block_tiles:
+                full = torch.empty(((n + qt - 1) // qt) * ((n + kt - 1) // kt), dtype=torch.uint8, device=dev)
+                _cabi.check(lib, lib.chill_mask_tabulate_blocks(ctypes.byref(desc), n, qt, kt, full.data_ptr(), st),
+                            "chill_mask_tabulate_blocks")
+                blocks[(qt, kt)] = full
+            torch.cuda.synchronize()
+        return {
+            "dense": dense.cpu().reshape(n, n).bool(), "k_lims": k_lims.cpu().long(), "q_lims": q_lims.cpu().long(),
+            "k_full": k_full.cpu().long(), "q_full": q_full.cpu().long(),
+            "blocks": {key: v.cpu().reshape((n + key[0] - 1) // key[0], -1).bool() for key, v in blocks.items()},
+            "traits": lib.chill_mask_traits(functor_id),
+        }
+
+    def verify(self, max_pos, device=False):
         """Consistency check of the whole contract on [0, max_pos)^2.
 
         Same checks as the reference (mask.py:700-803) - range functions equal
@@ -202,8 +244,18 @@ class ChillMask:
         ``is_full_block`` never claims a mixed tile, ``k_full_range_for_q`` only
         covers visible keys - plus the one the reference omits:
         ``q_full_range_for_k`` only covers queries that see the whole key tile.
+
+        ``device=False`` checks the Python functions of this class.  ``device=True`` checks the CUDA functor the
+        kernels are compiled with (the reference verifies the very functions its kernels inline): the functor is
+        tabulated on the GPU (``device_tables``), its mask and range tables must EQUAL this class's Python
+        functions, its host predicates must equal the class's, and its own full ranges / ``is_full_block`` must
+        hold against its own mask.  A functor whose ``k_range_for_q`` is off by one would silently drop keys in
+        the kernels; here it raises.
         """
         cls = type(self)
+        if device:
+            self._verify_device(max_pos)
+            return
         mask = self.make_mask(max_pos, device="cpu")
         assert mask.dtype == torch.bool, "Mask must be boolean"
         n = max_pos
@@ -255,6 +307,55 @@ class ChillMask:
                         assert mask[lo:hi, kb:ke].all(), (
                             f"q_full_range_for_k [{lo},{hi}) for k tile [{kb},{ke}) has masked pairs"
                         )
+
+    def _verify_device(self, max_pos):
+        cls = type(self)
+        n = int(max_pos)
+        self.verify(n)  # the Python half first: the device half is compared with it
+        py_mask = self.make_mask(n, device="cpu")
+        idx = torch.arange(n)
+        tiles = (16, 32, 64, 128)
+        block_tiles = [(a, b) for a in (16, 64, 128) for b in (16, 64, 128)]
+        base = self.device_tables(n, tiles[0], block_tiles)
+        dense = base["dense"]
+        bad = (dense != py_mask).nonzero()
+        assert bad.numel() == 0, (
+            f"{self.name}: CUDA functor mask() differs from the Python mask at (q, k) = {tuple(bad[0].tolist())}"
+        )
+        for what, table, fn in (("k_range_for_q", base["k_lims"], cls.k_range_for_q),
+                                ("q_range_for_k", base["q_lims"], cls.q_range_for_k)):
+            lo, hi = fn(idx, n, self.constargs)
+            exp = torch.stack([torch.as_tensor(lo).expand(n), torch.as_tensor(hi).expand(n)], 1).long()
+            # compare where the row / column sees anything at all (an empty range may be written in several ways)
+            seen = py_mask.any(dim=1) if what == "k_range_for_q" else py_mask.any(dim=0)
+            got = torch.minimum(table, torch.tensor(n - 1))
+            exp = torch.minimum(exp, torch.tensor(n - 1))
+            bad = (seen[:, None] & (got != exp)).any(dim=1).nonzero()
+            assert bad.numel() == 0, (
+                f"{self.name}: CUDA functor {what} differs from the Python function at position {int(bad[0])}: "
+                f"device {table[int(bad[0])].tolist()} vs python {exp[int(bad[0])].tolist()}"
+            )
+        tr = base["traits"]
+        for bit, fn in ((1, cls.has_k_full_range), (2, cls.has_q_full_range), (4, cls.k_lims_continious),
+                        (8, cls.q_lims_continious), (16, cls.is_guaranteed_safe)):
+            assert bool(tr & bit) == bool(fn()), f"{self.name}: CUDA functor flag {fn.__name__} = {bool(tr & bit)}, Python says {fn()}"
+        for (qt, kt), full in base["blocks"].items():
+            for qi, ki in full.nonzero().tolist():
+                tile = dense[qi * qt:(qi + 1) * qt, ki * kt:(ki + 1) * kt]
+                assert tile.all() or (~tile).all(), (
+                    f"{self.name}: CUDA is_full_block claims a mixed tile: q={qi * qt} k={ki * kt} q_tile={qt} k_tile={kt}"
+                )
+        for t in tiles:
+            tab = base if t == tiles[0] else self.device_tables(n, t)
+            for name, flag, key in (("k_full_range_for_q", tr & 1, "k_full"), ("q_full_range_for_k", tr & 2, "q_full")):
+                if not flag:
+                    continue
+                for i, (lo, hi) in enumerate(tab[key].tolist()):
+                    b, e = i * t, min(i * t + t, n)
+                    lo, hi = max(lo, 0), min(hi, n)
+                    if hi > lo:
+                        sub = dense[b:e, lo:hi] if key == "k_full" else dense[lo:hi, b:e]
+                        assert sub.all(), f"{self.name}: CUDA {name} [{lo},{hi}) for tile [{b},{e}) (size {t}) has masked pairs"
 
     def _flex(self, max_pos):
         from torch.nn.attention.flex_attention import create_block_mask

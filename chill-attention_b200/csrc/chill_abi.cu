@@ -464,6 +464,38 @@ static int noalloc_scratch(float** out) {
   return CHILL_OK;
 }
 
+// Self-test of the give-up path (chill_selftest_bounded_wait): the role structure of the tensor-core kernels in
+// miniature.  Warp 0 owns a TMEM allocation and plays the producer, every other warp a consumer; all of them wait on
+// an mbarrier that is initialised but never arrived at.  The first waiter whose limit runs out records the code and
+// raises the CTA's abort flag, the others see the flag and leave, TMEM is released and the kernel returns.
+__global__ void __launch_bounds__(128) selftest_bounded_wait_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar = tc::smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    tc::mbar_init(bar, 1);
+    tc::fence_barrier_init();
+  }
+  if (warp == 0) {
+    tc::tmem_alloc(tc::smem_u32(&tmem_slot), 32);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const tc::Guard guard{status, &abort_flag};
+  bool ok = true;
+  if (lane == 0) ok = tc::mbar_wait(bar, 0, guard, tc::kStSelfTest, limit_ns + (unsigned long long)warp * 1000ull);
+  ok = __all_sync(0xffffffffu, ok);  // the warp leaves together, as the kernels' roles do
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem_slot, 32);
+  (void)ok;
+}
+
 template <class M>
 static int traits_of() {
   return (M::kHasKFullRange ? 1 : 0) | (M::kHasQFullRange ? 2 : 0) | (M::kKLimsContinuous ? 4 : 0) |
@@ -571,6 +603,30 @@ int chill_mask_tabulate(const chill_mask_desc* m, int32_t n, int32_t tile, uint8
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) g_launches += 1;
   return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "mask_tabulate launch");
+}
+
+int chill_mask_tabulate_blocks(const chill_mask_desc* m, int32_t n, int32_t q_tile, int32_t k_tile, uint8_t* full,
+                               void* stream) {
+  if (m == nullptr || full == nullptr || n <= 0 || q_tile <= 0 || k_tile <= 0 || n > 32768) return CHILL_E_INVALID;
+  MaskArgs a = to_mask_args(*m, n);
+  const long long total = (long long)((n + q_tile - 1) / q_tile) * ((n + k_tile - 1) / k_tile);
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  cudaStream_t st = (cudaStream_t)stream;
+  CHILL_MASK_SWITCH(m->id, (mask_tabulate_blocks_kernel<MaskT><<<blocks, threads, 0, st>>>(a, n, q_tile, k_tile, full)))
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) g_launches += 1;
+  return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "mask_tabulate_blocks launch");
+}
+
+int chill_selftest_bounded_wait(int32_t limit_us, void* stream) {
+  int* status = device_status_ptr();
+  if (status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
+  const long long us = limit_us < 10 ? 10 : (limit_us > 100000 ? 100000 : limit_us);
+  selftest_bounded_wait_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(status, (unsigned long long)us * 1000ull);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) g_launches += 1;
+  return e == cudaSuccess ? CHILL_OK : cuda_fail(e, "selftest launch");
 }
 
 int chill_mask_traits(int32_t mask_id) {

@@ -427,4 +427,14 @@ __global__ void mask_tabulate_kernel(MaskArgs a, int n, int tile, uint8_t* dense
   }
 }
 
+template <class M>
+__global__ void mask_tabulate_blocks_kernel(MaskArgs a, int n, int q_tile, int k_tile, uint8_t* full) {
+  const int nq = (n + q_tile - 1) / q_tile, nk = (n + k_tile - 1) / k_tile;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < (long long)nq * nk) {
+    const int qi = (int)(idx / nk), ki = (int)(idx % nk);
+    full[idx] = M::is_full_block(qi * q_tile, ki * k_tile, q_tile, k_tile, n, a) ? 1 : 0;
+  }
+}
+
 }  // namespace chill

@@ -59,6 +59,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr int kStSelfTest = 901;  // CHILL_SELFTEST_STATUS
 
 // What every role needs to give up cleanly.
 struct Guard {
@@ -66,8 +67,9 @@ struct Guard {
   volatile int* abort; // CTA-shared flag
 };
 
-// Bounded wait.  `code` identifies the waiter in the status word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Guard& g, int code) {
+// Bounded wait.  `code` identifies the waiter in the status word; `limit_ns` is the time after which it gives up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Guard& g, int code,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -76,7 +78,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const G
       if (*g.abort) return false;
       const uint64_t t = globaltimer_ns();
       if (t0 == 0) t0 = t;
-      else if (t - t0 > kWaitLimitNs) {
+      else if (t - t0 > limit_ns) {
         atomicCAS(g.status, 0, code);
         *g.abort = 1;
         return false;

@@ -218,6 +218,13 @@ int chill_bwd_uses_tensor_cores(const chill_bwd_args* a);
 int chill_mask_tabulate(const chill_mask_desc* m, int32_t n, int32_t tile, uint8_t* dense, int32_t* k_lims,
                         int32_t* q_lims, int32_t* k_full, int32_t* q_full, void* stream);
 
+/* is_full_block of a functor on the tile grid of [0, n)^2 with seq_len = n (device pointer, optional stream):
+ *   full  uint8[ceil(n/q_tile) * ceil(n/k_tile)]   is_full_block(qi*q_tile, ki*k_tile, q_tile, k_tile, n), row = query tile
+ * Together with chill_mask_tabulate this is what ChillMask.verify(n, device=True) checks a CUDA functor with; the
+ * reference verifies the very functions its kernels inline the same way (mask.py:700-803, :487-534). */
+int chill_mask_tabulate_blocks(const chill_mask_desc* m, int32_t n, int32_t q_tile, int32_t k_tile, uint8_t* full,
+                               void* stream);
+
 /* Host-side properties of a functor: bit0 has_k_full_range, bit1 has_q_full_range,
  * bit2 k_lims_continious, bit3 q_lims_continious, bit4 is_guaranteed_safe. */
 int chill_mask_traits(int32_t mask_id);
@@ -229,6 +236,14 @@ int chill_read_device_status(void);
 /* Number of kernels this library has launched in the calling process so far (all devices, all streams;
  * memsets and copies are not counted).  A benchmark reads it before and after a timed region. */
 unsigned long long chill_launch_count(void);
+
+/* Self-test of the give-up path of the kernels' bounded waits.  Launches one small kernel in which every role waits,
+ * with a limit of `limit_us` microseconds (clamped to [10, 100000]), on an mbarrier that nothing ever arrives at; the
+ * waits run out, the kernel records CHILL_SELFTEST_STATUS in the device status word, releases its TMEM and returns.
+ * Nothing faults or hangs and the context stays usable; afterwards chill_read_device_status() returns
+ * CHILL_SELFTEST_STATUS once.  Returns 0 if the kernel was launched.  No counterpart in the reference. */
+#define CHILL_SELFTEST_STATUS 901
+int chill_selftest_bounded_wait(int32_t limit_us, void* stream);
 
 int chill_abi_version(void);
 const char* chill_status_string(int status);

@@ -274,3 +274,27 @@ def test_fp32_forward_in_tf32_with_lens_and_ragged_length(_lib):
         fin = torch.isfinite(lse_ref)
         assert torch.equal(torch.isfinite(lse.cpu()), fin)
         assert ((lse.cpu().double() - lse_ref)[fin].abs() / lse_ref[fin].abs().clamp(min=1.0)).max().item() <= 3e-3
+
+
+def test_a_bounded_wait_that_runs_out_ends_as_a_status_code(_lib):
+    """The give-up path of the kernels' bounded mbarrier waits, exercised without faulting or hanging anything:
+    a small kernel whose roles all wait (1 ms limit) on a barrier nobody arrives at must return, release its
+    TMEM, leave its code in the device status word, and leave the context fully usable."""
+    import time
+
+    import chill_attention as ca
+    from chill_attention import _cabi
+
+    assert _lib.chill_read_device_status() == 0
+    t0 = time.perf_counter()
+    assert _lib.chill_selftest_bounded_wait(1000, None) == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0, "the waits are bounded by their limit, not by the 2 s default"
+    assert _lib.chill_read_device_status() == _cabi.SELFTEST_STATUS
+    assert _lib.chill_read_device_status() == 0, "reading the status clears it"
+    # the context, the TMEM allocator and the kernels are unaffected
+    q, k, v, do = make_inputs(1, 2, 2, 256, 128, torch.bfloat16, seed=77)
+    o, lse, grads = run(ca.CausalChillMask(), q, k, v, do)
+    o_ref, lse_ref, *g_ref = oracle_all(ca.CausalChillMask(), q, k, v, do)
+    check_forward(o, lse, o_ref, lse_ref, None, torch.bfloat16)
+    check_grads(grads, g_ref, torch.bfloat16)
