@@ -441,8 +441,9 @@ def run_ours(args):
         tiny = time_public_op(ca, mask, (8, 4, 128, 128), torch.float16, dev, 50)
         op_ms = {"fwd": round(big["fwd"], 4), "bwd": round(big["bwd"], 4), "fwd_bwd": round(big["fwd"] + big["bwd"], 4),
                  "t128_fwd_us": round(tiny["fwd"] * 1e3, 1), "t128_bwd_us": round(tiny["bwd"] * 1e3, 1),
-                 "note": "chill_attention() and .backward() through the dispatcher ops, outputs and scratch allocated "
-                         "inside the call; t128 = (8, 4, 128, 128) fp16, one call each"}
+                 "note": "chill_attention() and .backward() as a user calls them in eager mode, outputs and scratch "
+                         "allocated inside the call; t128 = (8, 4, 128, 128) fp16, one call each (the backward figure "
+                         "includes autograd's engine and the accumulation into three .grad tensors)"}
 
     # ---- end to end through the public API with host buffers
     e2e = None

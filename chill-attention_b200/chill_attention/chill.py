@@ -24,7 +24,7 @@ import typing
 
 import torch
 
-from . import _cabi
+from . import _cabi, _eager
 from .mask import ChillMask
 
 logger = logging.getLogger(__name__)
@@ -47,9 +47,20 @@ def _backward_operand(do: torch.Tensor) -> torch.Tensor:
     return do if _cabi.tma_compatible(do) else do.contiguous()
 
 
+def _tensor_core_operands(q, k, v):
+    """16-bit q, k, v with a head dimension the tensor-core kernels serve, but in a memory layout TMA cannot describe
+    (channel stride != 1, a broadcast dimension, rows not 16-byte aligned): one packing copy each puts them on the
+    tensor-core path, ~1000x faster than the generic kernels that would otherwise take the call.  The reference reads
+    such tensors through block pointers at full speed (chill_fwd.py:74-98); results are identical either way."""
+    if q.dtype == torch.float32 or q.shape[-1] not in (64, 128):
+        return q, k, v
+    return tuple(t if _cabi.tma_compatible(t) else t.contiguous() for t in (q, k, v))
+
+
 def _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scale, d_lse=None):
     import ctypes as C
 
+    q, k, v = _tensor_core_operands(q, k, v)
     with torch.cuda.device(q.device):
         do = _backward_operand(do)
         delta = torch.empty(o.shape[:-1], dtype=torch.float32, device=o.device)
@@ -108,7 +119,7 @@ def register_chill_mask(mask: ChillMask):
     if hasattr(torch.ops.chill_attention, f"forward{mask_name}"):
         return
     lib, functor_id = _resolve_functor(mask)
-    _REGISTRY[mask_name] = (lib, functor_id)
+    _REGISTRY[mask_name] = (lib, functor_id)  # also what the eager call path (_eager.py) looks up
 
     @torch.library.custom_op(f"chill_attention::forward{mask_name}", mutates_args=(), device_types=("cuda",))
     def attention_forward_adapter(
@@ -124,6 +135,7 @@ def register_chill_mask(mask: ChillMask):
         autotune: bool,
     ) -> tuple[torch.Tensor, torch.Tensor]:
         _check_inputs(q, k, v, lens, sm_scale)
+        q, k, v = _tensor_core_operands(q, k, v)
         with torch.cuda.device(q.device):
             O = torch.empty_like(q, memory_format=torch.contiguous_format)
             LSE = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if return_lse else None
@@ -288,13 +300,22 @@ def chill_attention(
 
     Returns: O, or (O, LSE) when ``return_lse``.
     """
-    register_chill_mask(mask)
-    if not torch.compiler.is_compiling():
-        for i in (q, k, v):
-            torch._dynamo.mark_static(i, 1)
-            torch._dynamo.mark_static(i, 3)
+    entry = _REGISTRY.get(mask.name)
+    if entry is None:
+        register_chill_mask(mask)
+        entry = _REGISTRY.get(mask.name)
     if sm_scale is None:
         sm_scale = 1.0 / (q.shape[-1] ** 0.5)
+    compiling = torch.compiler.is_compiling()
+    if not compiling and entry is not None and _eager.usable(q, k, v, lens):
+        # plain eager call: same kernels through the short host path (see _eager.py), which validates the arguments
+        flags = _cabi.FLAG_ALLOW_TF32 if (precision == "tf32" and q.dtype == torch.float32) else 0
+        return _eager.attention(entry, q, k, v, lens, mask.constargs, float(sm_scale), bool(return_lse), flags)
+    if not compiling:
+        for i in (q, k, v):
+            if getattr(i, "_dynamo_static_indices", None) != {1, 3}:
+                torch._dynamo.mark_static(i, 1)
+                torch._dynamo.mark_static(i, 3)
     return _chill_attention(
         q=q, k=k, v=v, lens=lens, mask_name=mask.name, mask_args=mask.constargs, sm_scale=sm_scale,
         return_lse=return_lse, prescale_qk=prescale_qk, precision=precision, autotune=autotune,

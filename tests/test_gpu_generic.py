@@ -91,13 +91,21 @@ def test_noncontiguous_inputs(dtype):
 
     from chill_attention import chill_attention
 
+    from chill_attention import chill as chill_mod
+
     qd, kd, vd = (strided(t).requires_grad_(True) for t in (q, k, v))
     assert qd.stride(-1) == 2
+    before = chill_mod.backward_path_counts()
     o, lse = chill_attention(qd, kd, vd, mask=mask, return_lse=True)
     o.backward(do.cuda())
     assert o.is_contiguous()
     check_forward(o, lse, o_ref, lse_ref, None, dtype)
     check_grads((qd.grad, kd.grad, vd.grad), g_ref, dtype)
+    # 16-bit operands with a head dimension the tensor-core kernels serve are packed once and stay on that path;
+    # fp32 is read in place through its strides by the generic kernels
+    after = chill_mod.backward_path_counts()
+    which = "generic" if dtype == torch.float32 else "tensor_core"
+    assert after[which] == before[which] + 1
 
 
 def test_sm_scale_and_no_lse():

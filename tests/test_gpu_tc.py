@@ -298,3 +298,39 @@ def test_a_bounded_wait_that_runs_out_ends_as_a_status_code(_lib):
     o_ref, lse_ref, *g_ref = oracle_all(ca.CausalChillMask(), q, k, v, do)
     check_forward(o, lse, o_ref, lse_ref, None, torch.bfloat16)
     check_grads(grads, g_ref, torch.bfloat16)
+
+
+def test_eager_call_path_equals_the_dispatcher_ops(_lib):
+    """chill_attention() in plain eager mode takes the short host path (_eager.py); the dispatcher ops that
+    torch.compile graphs use must give the same bits (same kernels, same arguments), forward and backward,
+    with and without lens / return_lse, and with a gradient arriving at the LSE."""
+    import chill_attention as ca
+    from chill_attention import _cabi, _eager, chill
+
+    mask = ca.SlidingWindowChillMask(100, 7)
+    q, k, v, do = make_inputs(2, 4, 2, 333, 128, torch.bfloat16, seed=78)
+    lens = torch.tensor([333, 150], dtype=torch.int32).cuda()
+    before = _cabi._deterministic
+    ca.set_deterministic(True)  # bitwise comparable dQ
+    try:
+        for ln in (None, lens):
+            outs = []
+            for fast in (True, False):
+                qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+                assert _eager.usable(qd, kd, vd, ln)
+                if fast:
+                    o, lse = ca.chill_attention(qd, kd, vd, mask=mask, lens=ln, return_lse=True)
+                else:
+                    o, lse = chill._chill_attention(q=qd, k=kd, v=vd, lens=ln, mask_name=mask.name, mask_args=mask.constargs,
+                                                    sm_scale=128 ** -0.5, return_lse=True, prescale_qk=False,
+                                                    precision="ieee", autotune=False)
+                (o.float() * do.cuda().float()).sum().add(lse.sum() * 0.01).backward()
+                outs.append((o.detach(), lse.detach(), qd.grad, kd.grad, vd.grad))
+            for x, y in zip(*outs):
+                assert torch.equal(x, y)
+    finally:
+        ca.set_deterministic(before)
+    # no-grad call: a single tensor comes back, nothing is recorded
+    with torch.no_grad():
+        o = ca.chill_attention(q.cuda(), k.cuda(), v.cuda(), mask=mask)
+    assert isinstance(o, torch.Tensor) and not o.requires_grad
