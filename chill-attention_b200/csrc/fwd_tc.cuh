@@ -55,6 +55,26 @@ constexpr int kFwdThreads = 256;      // warps 0-3 softmax, 4 TMA producer, 5 MM
 constexpr int kFwdSoftmaxRegs = 200;  // per-thread register budget after setmaxnreg (2 CTAs/SM:
 constexpr int kFwdOtherRegs = 56;     //   2 * 128 * (200 + 56) = 65536)
 constexpr int kTmemColsFwd = 256;
+
+// Shape of the 16-bit forward kernel for one head dimension.  The kernel is bound by the latency of its per-tile
+// chain S = Q K^T -> softmax -> O += P V (the next S overwrites P, so the steps of one CTA cannot overlap; measured
+// ~4100 clocks per 128-key tile per CTA against 1024 clocks of tensor work), so what counts is how many such chains an
+// SM runs side by side, which TMEM (512 columns: S + O per CTA) limits.  D = 128: S 128 + O 128 columns, two CTAs.
+// D = 64: key tiles of 64 keys need S 64 + O 64 = 128 columns, four CTAs; the narrower MMAs (N = 64) run at 2/3 of
+// the rate, which the kernel does not feel.  A CTA's register pool is threads x launch registers, and the softmax
+// warpgroup's setmaxnreg.inc is only ever granted if softmax + other <= 2 x launch.
+template <int D>
+struct FwdShape {
+  static constexpr int kKeys = (D == 64) ? 64 : 128;       // keys per tile
+  static constexpr int kCtasPerSm = (D == 64) ? 4 : 2;
+  static constexpr int kStages = (D == 64) ? 2 : 1;        // K / V ring depth
+  static constexpr int kTmemCols = (kKeys + D <= 128) ? 128 : 256;
+  static constexpr int kLaunchRegs = 65536 / (kCtasPerSm * kFwdThreads);   // 64 or 128
+  static constexpr int kSoftmaxRegs = (D == 64) ? 96 : 200;
+  static constexpr int kOtherRegs = (D == 64) ? 32 : 56;
+  static_assert(kSoftmaxRegs + kOtherRegs <= 2 * kLaunchRegs, "setmaxnreg.inc would never be granted");
+  static_assert(kCtasPerSm * kTmemCols <= 512, "TMEM columns of an SM");
+};
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdTcParams {
@@ -66,13 +86,14 @@ struct FwdTcParams {
   int* status;
 };
 
-template <int D, int NSTAGE>
+template <int D, int NSTAGE, int KT = kTile>
 struct FwdSmem {
-  static constexpr int kTileBytes = kTile * D * 2;  // one 128 x D tile of 16-bit elements
+  static constexpr int kTileBytes = kTile * D * 2;  // one 128 x D tile of 16-bit elements (Q)
+  static constexpr int kKvBytes = KT * D * 2;       // one K or V tile: KT keys
   static constexpr int kQ = 0;
   static constexpr int kK = kQ + kTileBytes;
-  static constexpr int kV = kK + NSTAGE * kTileBytes;
-  static constexpr int kBars = kV + NSTAGE * kTileBytes;
+  static constexpr int kV = kK + NSTAGE * kKvBytes;
+  static constexpr int kBars = kV + NSTAGE * kKvBytes;
   static constexpr int kNumBars = 4 + 4 * NSTAGE;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
@@ -85,7 +106,7 @@ enum : int { kStProducer = 101, kStMma = 102, kStSoftmax = 103, kStEpilogue = 10
 // Online-softmax step of one thread (= one query row) for one 128-key tile: reads the row of S from
 // TMEM, updates the running maximum / sum, rescales the O accumulator in TMEM when needed and writes the
 // 16-bit P row back over S.  `first` = first key tile of this row (no O to rescale yet).
-template <typename T, int D, class M>
+template <typename T, int D, class M, int KT = kTile>
 __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_sel, bool first, bool full, int klim,
                                              int qg, int kg0, int n, const MaskArgs& margs, float c, float& m_used,
                                              float& l) {
@@ -93,19 +114,19 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   // is taken with 3-input max on four independent chains, and exponentials, row sum and the
   // 16-bit packing run on pairs (packed fp32 FMA / ADD).  Full tiles skip the mask arithmetic
   // (separate copy of the body, so nothing is if-converted into the fast path).
-  uint32_t sreg[kTile];
+  uint32_t sreg[KT];
 #pragma unroll
-  for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tS + lane_sel + q4 * 32, sreg + q4 * 32);
+  for (int q4 = 0; q4 < KT / 32; ++q4) tmem_ld32(tS + lane_sel + q4 * 32, sreg + q4 * 32);
   tmem_wait_ld();
   if (!full) {
     if (interval_rows<M>::value) {  // two per-row bounds instead of a mask() call per element
       int c_lo, c_hi;
       row_window<M, true>(qg, kg0, klim, n, margs, c_lo, c_hi);
 #pragma unroll
-      for (int cidx = 0; cidx < kTile; ++cidx) sreg[cidx] = (cidx >= c_lo && cidx <= c_hi) ? sreg[cidx] : 0xff800000u;
+      for (int cidx = 0; cidx < KT; ++cidx) sreg[cidx] = (cidx >= c_lo && cidx <= c_hi) ? sreg[cidx] : 0xff800000u;
     } else {
 #pragma unroll
-      for (int cidx = 0; cidx < kTile; ++cidx) {
+      for (int cidx = 0; cidx < KT; ++cidx) {
         const bool vis = cidx < klim && M::mask(qg, kg0 + cidx, n, margs);
         sreg[cidx] = vis ? sreg[cidx] : 0xff800000u;  // -inf
       }
@@ -113,7 +134,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   }
   float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
 #pragma unroll
-  for (int i = 0; i < kTile; i += 8) {
+  for (int i = 0; i < KT; i += 8) {
     mx0 = fmax3(mx0, __uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1]));
     mx1 = fmax3(mx1, __uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3]));
     mx2 = fmax3(mx2, __uint_as_float(sreg[i + 4]), __uint_as_float(sreg[i + 5]));
@@ -144,7 +165,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   const uint64_t c2 = pk2(c, c), nm2 = pk2(-m_safe, -m_safe);
   uint64_t l0 = 0ull, l1 = 0ull;  // two packed partial row sums (+0.0f, +0.0f)
 #pragma unroll
-  for (int i = 0; i < kTile / 2; i += 2) {
+  for (int i = 0; i < KT / 2; i += 2) {
     // two pairs per step; a fixed share of the pairs takes the polynomial 2^x (FMA pipe), the rest MUFU
     const uint64_t e0 = ex2_pair(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nm2),
                                  (i % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
@@ -164,8 +185,8 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
     upk2(l1, a2, a3);
     l += (a0 + a1) + (a2 + a3);
   }
-  tmem_st32(tS + lane_sel, sreg);
-  tmem_st32(tS + lane_sel + 32, sreg + 32);
+#pragma unroll
+  for (int q4 = 0; q4 < KT / 64; ++q4) tmem_st32(tS + lane_sel + q4 * 32, sreg + q4 * 32);  // KT / 2 columns of 16-bit pairs
 }
 
 // Normalise this thread's O row, convert to 16 bits and stage it in the 128B-swizzled TMA box layout;
@@ -208,13 +229,17 @@ __device__ __forceinline__ void stage_output_row(uint8_t* sO, uint32_t tO, uint3
   }
 }
 
-template <typename T, int D, class M, int NSTAGE>
-__global__ void __launch_bounds__(kFwdThreads, 2)
+template <typename T, int D, class M>
+__global__ void __launch_bounds__(kFwdThreads, FwdShape<D>::kCtasPerSm)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, FwdTcParams p) {
-  using L = FwdSmem<D, NSTAGE>;
+  using SH = FwdShape<D>;
+  constexpr int NSTAGE = SH::kStages;
+  constexpr int KT = SH::kKeys;                // keys per tile
+  using L = FwdSmem<D, NSTAGE, KT>;
   constexpr int kChunks = D / 64;              // 64-channel (128-byte) column blocks per tile
-  constexpr int kChunkBytes = kTile * 128;     // one column block: 128 rows x 128 bytes
+  constexpr int kChunkBytes = kTile * 128;     // one column block of Q / O: 128 rows x 128 bytes
+  constexpr int kKvChunkBytes = KT * 128;      // one column block of a K / V tile: KT rows x 128 bytes
   const Geo& g = p.g;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (g.Lq + kTile - 1) / kTile;
@@ -243,7 +268,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   }
 
   // ---- key-tile range of this query tile (same arithmetic in every role)
-  int kt_lo = 0, kt_hi = 0;  // [kt_lo, kt_hi) in units of 128 local key rows
+  int kt_lo = 0, kt_hi = 0;  // [kt_lo, kt_hi) in units of KT local key rows
   int full_lo = 0, full_hi = 0;  // global, half-open: keys visible to every row of the tile
   {
     int lo, hi;
@@ -251,8 +276,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int lo_l = imax(lo - g.k_off, 0);
     const int hi_l = imin(imin(hi, n - 1) - g.k_off, g.Lk - 1);
     if (hi_l >= lo_l) {
-      kt_lo = lo_l / kTile;
-      kt_hi = hi_l / kTile + 1;
+      kt_lo = lo_l / KT;
+      kt_hi = hi_l / KT + 1;
     }
     if (M::kHasKFullRange) M::k_full_range_for_q(qg0, kTile, n, g.margs, full_lo, full_hi);
   }
@@ -290,14 +315,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (n_tiles > 0) {
         mbar_arrive_expect_tx(bar_q_full, L::kTileBytes);
         for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * kChunkBytes, &tmQ, bar_q_full, c * 64, qb, h, b);
-        mbar_arrive_expect_tx(bar_k_full, L::kTileBytes);
-        for (int c = 0; c < kChunks; ++c) tma_load_4d(sK + c * kChunkBytes, &tmK, bar_k_full, c * 64, kt_lo * kTile, hk, b);
-        mbar_arrive_expect_tx(bar_v_full, L::kTileBytes);
-        for (int c = 0; c < kChunks; ++c) tma_load_4d(sV + c * kChunkBytes, &tmV, bar_v_full, c * 64, kt_lo * kTile, hk, b);
+        mbar_arrive_expect_tx(bar_k_full, L::kKvBytes);
+        for (int c = 0; c < kChunks; ++c) tma_load_4d(sK + c * kKvChunkBytes, &tmK, bar_k_full, c * 64, kt_lo * KT, hk, b);
+        mbar_arrive_expect_tx(bar_v_full, L::kKvBytes);
+        for (int c = 0; c < kChunks; ++c) tma_load_4d(sV + c * kKvChunkBytes, &tmV, bar_v_full, c * 64, kt_lo * KT, hk, b);
       }
     }
     __syncwarp();
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColsFwd);
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), SH::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -305,27 +330,27 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem;            // S / P columns
-  const uint32_t tO = tmem + kTile;    // O columns
+  const uint32_t tO = tmem + KT;       // O columns
 
   if (warp == 4) {
-    reg_dealloc<kFwdOtherRegs>();
+    reg_dealloc<SH::kOtherRegs>();
     // ------------------------------------------------------------------- TMA producer
     if (lane == 0 && n_tiles > 0) {
       bool ok = true;
       for (int j = 1; j < n_tiles && ok; ++j) {  // tile 0 was issued during set-up
         const int s = j % NSTAGE;
         const uint32_t ph = (uint32_t)(j / NSTAGE) & 1u;
-        const int krow = (kt_lo + j) * kTile;
+        const int krow = (kt_lo + j) * KT;
         ok = mbar_wait(bar_k_empty + 8 * s, ph ^ 1u, guard, kStProducer);
         if (!ok) break;
-        mbar_arrive_expect_tx(bar_k_full + 8 * s, L::kTileBytes);
+        mbar_arrive_expect_tx(bar_k_full + 8 * s, L::kKvBytes);
         for (int c = 0; c < kChunks; ++c)
-          tma_load_4d(sK + s * L::kTileBytes + c * kChunkBytes, &tmK, bar_k_full + 8 * s, c * 64, krow, hk, b);
+          tma_load_4d(sK + s * L::kKvBytes + c * kKvChunkBytes, &tmK, bar_k_full + 8 * s, c * 64, krow, hk, b);
         ok = mbar_wait(bar_v_empty + 8 * s, ph ^ 1u, guard, kStProducer);
         if (!ok) break;
-        mbar_arrive_expect_tx(bar_v_full + 8 * s, L::kTileBytes);
+        mbar_arrive_expect_tx(bar_v_full + 8 * s, L::kKvBytes);
         for (int c = 0; c < kChunks; ++c)
-          tma_load_4d(sV + s * L::kTileBytes + c * kChunkBytes, &tmV, bar_v_full + 8 * s, c * 64, krow, hk, b);
+          tma_load_4d(sV + s * L::kKvBytes + c * kKvChunkBytes, &tmV, bar_v_full + 8 * s, c * 64, krow, hk, b);
       }
       if (!ok) {
         // give copies already in flight time to land before the CTA's shared memory goes away
@@ -334,10 +359,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
     }
   } else if (warp == 5) {
-    reg_dealloc<kFwdOtherRegs>();
+    reg_dealloc<SH::kOtherRegs>();
     // --------------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_tiles > 0) {
-      constexpr uint32_t idesc_s = make_idesc<T>(kTile, kTile, false, false);
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, KT, false, false);
       constexpr uint32_t idesc_o = make_idesc<T>(kTile, D, false, true);
       constexpr uint32_t hi_k = desc_hi_sw128(1024);  // both operand kinds: 8-row groups 1 KB apart
       const uint32_t q_lo = desc_lo_sw128(sQ, 16);
@@ -345,15 +370,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % NSTAGE;
         const uint32_t ph = (uint32_t)(j / NSTAGE) & 1u;
-        const uint32_t k_lo = desc_lo_sw128(sK + s * L::kTileBytes, 16);
-        const uint32_t v_lo = desc_lo_sw128(sV + s * L::kTileBytes, kChunkBytes);  // MN-major: channel blocks 16 KB apart
+        const uint32_t k_lo = desc_lo_sw128(sK + s * L::kKvBytes, 16);
+        const uint32_t v_lo = desc_lo_sw128(sV + s * L::kKvBytes, kKvChunkBytes);  // MN-major: channel blocks one chunk apart
         ok = mbar_wait(bar_k_full + 8 * s, ph, guard, kStMma);
         if (!ok) break;
         tc_fence_after();
         // S = Q K^T: both K-major; 16 channels (32 bytes) per instruction.
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss_lh(tS, q_lo + kmajor_step(kk), k_lo + kmajor_step(kk), hi_k, idesc_s, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < D / 16; ++kk)  // Q chunks are 128 rows apart, K chunks KT rows
+          mma_ss_lh(tS, q_lo + kmajor_step(kk), k_lo + (uint32_t)((kk / 4) * (kKvChunkBytes / 16) + (kk % 4) * 2), hi_k, idesc_s,
+                    kk > 0 ? 1u : 0u);
         mma_commit(bar_k_empty + 8 * s);
         mma_commit(bar_s_full);
         ok = mbar_wait(bar_p_full, (uint32_t)j & 1u, guard, kStMma);
@@ -363,16 +389,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         tc_fence_after();
         // O += P V: P (128 x 128, 16-bit) from TMEM, 16 keys = 8 columns and 2 KB of V per instruction.
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
+        for (int kk = 0; kk < KT / 16; ++kk)
           mma_ts_lh(tO, tS + kk * 8, v_lo + kk * 128, hi_k, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         mma_commit(bar_v_empty + 8 * s);
       }
       if (ok) mma_commit(bar_o_full);
     }
   } else if (warp >= 6) {
-    reg_dealloc<kFwdOtherRegs>();  // idle warps of the second warpgroup only give their registers back
+    reg_dealloc<SH::kOtherRegs>();  // idle warps of the second warpgroup only give their registers back
   } else {
-    reg_alloc<kFwdSoftmaxRegs>();
+    reg_alloc<SH::kSoftmaxRegs>();
     // --------------------------------------------------------- softmax + epilogue warps
     const int r = warp * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
@@ -382,15 +408,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int kt = kt_lo + j;
-      const int kg0 = kt * kTile + g.k_off;
+      const int kg0 = kt * KT + g.k_off;
       ok = mbar_wait(bar_s_full, (uint32_t)j & 1u, guard, kStSoftmax);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
-      const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + kTile <= full_hi && kg0 + kTile <= n &&
-                        kt * kTile + kTile <= g.Lk;
-      const int klim = imin(n - kg0, g.Lk - kt * kTile);  // columns >= klim do not exist
-      softmax_tile<T, D, M>(tS, tO, lane_sel, j == 0, full, klim, qg, kg0, n, g.margs, c, m_used, l);
+      const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + KT <= full_hi && kg0 + KT <= n &&
+                        kt * KT + KT <= g.Lk;
+      const int klim = imin(n - kg0, g.Lk - kt * KT);  // columns >= klim do not exist
+      softmax_tile<T, D, M, KT>(tS, tO, lane_sel, j == 0, full, klim, qg, kg0, n, g.margs, c, m_used, l);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -416,7 +442,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, kTmemColsFwd);
+  if (warp == 4) tmem_dealloc(tmem, SH::kTmemCols);
 }
 
 }  // namespace tc

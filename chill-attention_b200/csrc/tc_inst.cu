@@ -14,10 +14,12 @@ namespace chill {
 
 using InstMask = CHILL_INST_MASK;
 
-template <typename T, int D, int NSTAGE>
+template <typename T, int D>
 static int launch_fwd_one(const CUtensorMap* maps, const tc::FwdTcParams& p, dim3 grid, cudaStream_t st) {
-  auto kern = tc::fwd_tc_kernel<T, D, InstMask, NSTAGE>;
-  constexpr int smem = tc::FwdSmem<D, NSTAGE>::kDynamic;
+  auto kern = tc::fwd_tc_kernel<T, D, InstMask>;
+  using SH = tc::FwdShape<D>;
+  constexpr int smem = tc::FwdSmem<D, SH::kStages, SH::kKeys>::kDynamic;
+  static_assert(SH::kCtasPerSm * smem <= 232448, "the CTAs that are to share an SM must fit its shared memory");
   struct Tag {};
   cudaError_t e = ensure_dynamic_smem<Tag>(kern, smem, /*prefer_max_carveout=*/true);
   if (e != cudaSuccess) return (int)e;
@@ -29,11 +31,11 @@ template <>
 int tc_launch_fwd<InstMask>(int dtype, int D, const CUtensorMap* maps, const tc::FwdTcParams& p, dim3 grid,
                             cudaStream_t st) {
   if (dtype == 2) {
-    if (D == 128) return launch_fwd_one<__nv_bfloat16, 128, 1>(maps, p, grid, st);
-    if (D == 64) return launch_fwd_one<__nv_bfloat16, 64, 2>(maps, p, grid, st);
+    if (D == 128) return launch_fwd_one<__nv_bfloat16, 128>(maps, p, grid, st);
+    if (D == 64) return launch_fwd_one<__nv_bfloat16, 64>(maps, p, grid, st);
   } else if (dtype == 1) {
-    if (D == 128) return launch_fwd_one<__half, 128, 1>(maps, p, grid, st);
-    if (D == 64) return launch_fwd_one<__half, 64, 2>(maps, p, grid, st);
+    if (D == 128) return launch_fwd_one<__half, 128>(maps, p, grid, st);
+    if (D == 64) return launch_fwd_one<__half, 64>(maps, p, grid, st);
   }
   return (int)cudaErrorInvalidValue;
 }
