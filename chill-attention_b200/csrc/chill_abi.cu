@@ -189,9 +189,15 @@ static bool shape_tf32_ok(const chill_shape& s) {
   return s.dtype == CHILL_F32 && (s.flags & CHILL_FLAG_ALLOW_TF32) && (s.D == 64 || s.D == 128) && s.sm_scale > 0.f;
 }
 
+// the forward also has a tensor-core kernel for 16-bit head dim 256 (one CTA per SM); the backward does not
+static bool shape_tc_fwd_only_ok(const chill_shape& s) {
+  if (s.flags & CHILL_FLAG_FORCE_GENERIC) return false;
+  return (s.dtype == CHILL_F16 || s.dtype == CHILL_BF16) && s.D == 256 && s.sm_scale > 0.f;
+}
+
 static bool fwd_tc_eligible(const chill_fwd_args& a) {
   const chill_shape& s = a.s;
-  if (!shape_tc_ok(s) && !shape_tf32_ok(s)) return false;
+  if (!shape_tc_ok(s) && !shape_tf32_ok(s) && !shape_tc_fwd_only_ok(s)) return false;
   const size_t es = esize(s.dtype);
   return tma_ok(a.q, a.q_strides, s.B, s.H, s.Lq, es) && tma_ok(a.k, a.k_strides, s.B, s.H_kv, s.Lk, es) &&
          tma_ok(a.v, a.v_strides, s.B, s.H_kv, s.Lk, es) && tma_ok(a.o, a.o_strides, s.B, s.H, s.Lq, es);

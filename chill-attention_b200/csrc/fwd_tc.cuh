@@ -63,13 +63,14 @@ constexpr int kTmemColsFwd = 256;
 // D = 64: key tiles of 64 keys need S 64 + O 64 = 128 columns, four CTAs; the narrower MMAs (N = 64) run at 2/3 of
 // the rate, which the kernel does not feel.  A CTA's register pool is threads x launch registers, and the softmax
 // warpgroup's setmaxnreg.inc is only ever granted if softmax + other <= 2 x launch.
+// D = 256: S 128 + O 256 columns and 192 KB of Q / K / V tiles leave room for one CTA per SM only.
 template <int D>
 struct FwdShape {
   static constexpr int kKeys = (D == 64) ? 64 : 128;       // keys per tile
-  static constexpr int kCtasPerSm = (D == 64) ? 4 : 2;
+  static constexpr int kCtasPerSm = (D == 64) ? 4 : (D == 128 ? 2 : 1);
   static constexpr int kStages = (D == 64) ? 2 : 1;        // K / V ring depth
-  static constexpr int kTmemCols = (kKeys + D <= 128) ? 128 : 256;
-  static constexpr int kLaunchRegs = 65536 / (kCtasPerSm * kFwdThreads);   // 64 or 128
+  static constexpr int kTmemCols = (kKeys + D <= 128) ? 128 : (kKeys + D <= 256 ? 256 : 512);
+  static constexpr int kLaunchRegs = (65536 / (kCtasPerSm * kFwdThreads) > 128) ? 128 : 65536 / (kCtasPerSm * kFwdThreads);
   static constexpr int kSoftmaxRegs = (D == 64) ? 96 : 200;
   static constexpr int kOtherRegs = (D == 64) ? 32 : 56;
   static_assert(kSoftmaxRegs + kOtherRegs <= 2 * kLaunchRegs, "setmaxnreg.inc would never be granted");
@@ -230,7 +231,7 @@ __device__ __forceinline__ void stage_output_row(uint8_t* sO, uint32_t tO, uint3
 }
 
 template <typename T, int D, class M>
-__global__ void __launch_bounds__(kFwdThreads, FwdShape<D>::kCtasPerSm)
+__global__ void __launch_bounds__(kFwdThreads, (FwdShape<D>::kCtasPerSm > 1 ? FwdShape<D>::kCtasPerSm : 2))
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, FwdTcParams p) {
   using SH = FwdShape<D>;

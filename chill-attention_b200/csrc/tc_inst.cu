@@ -33,9 +33,11 @@ int tc_launch_fwd<InstMask>(int dtype, int D, const CUtensorMap* maps, const tc:
   if (dtype == 2) {
     if (D == 128) return launch_fwd_one<__nv_bfloat16, 128>(maps, p, grid, st);
     if (D == 64) return launch_fwd_one<__nv_bfloat16, 64>(maps, p, grid, st);
+    if (D == 256) return launch_fwd_one<__nv_bfloat16, 256>(maps, p, grid, st);
   } else if (dtype == 1) {
     if (D == 128) return launch_fwd_one<__half, 128>(maps, p, grid, st);
     if (D == 64) return launch_fwd_one<__half, 64>(maps, p, grid, st);
+    if (D == 256) return launch_fwd_one<__half, 256>(maps, p, grid, st);
   }
   return (int)cudaErrorInvalidValue;
 }

@@ -59,6 +59,22 @@ def test_dispatch_takes_the_tensor_core_path(_lib):
     assert uses_tc(_lib, q32, q32, q32, ca.CausalChillMask()) == 0
     q16 = torch.zeros(1, 2, 256, 16, dtype=torch.bfloat16, device="cuda")
     assert uses_tc(_lib, q16, q16, q16, ca.CausalChillMask()) == 0
+    q256 = torch.zeros(1, 2, 256, 256, dtype=torch.float16, device="cuda")
+    assert uses_tc(_lib, q256, q256, q256, ca.CausalChillMask()) == 1  # forward only: one CTA per SM
+
+
+@pytest.mark.parametrize("mask", big_masks(), ids=str)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+@pytest.mark.parametrize("L", [128, 700])
+def test_forward_head_dim_256_on_the_tensor_cores(mask, dtype, L, _lib):
+    """Head dim 256: the forward runs the tcgen05 kernel (S 128 + O 256 TMEM columns, one CTA per SM); the backward
+    of this shape is served by the generic kernels and is covered in test_gpu_generic.py."""
+    q, k, v, do = make_inputs(2, 4, 2, L, 256, dtype, seed=79)
+    lens = torch.tensor([L, max(1, L // 3)], dtype=torch.int32)
+    assert uses_tc(_lib, q.cuda(), k.cuda(), v.cuda(), mask) == 1
+    o_ref, lse_ref, *_ = oracle_all(mask, q, k, v, do, lens)
+    o, lse, _ = run(mask, q, k, v, do, lens, backward=False)
+    check_forward(o, lse, o_ref, lse_ref, lens, dtype)
 
 
 @pytest.mark.parametrize("mask", big_masks(), ids=str)
