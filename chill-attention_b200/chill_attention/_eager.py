@@ -100,14 +100,14 @@ def _forward(entry, q, k, v, lens, mask_args, sm_scale, want_lse, flags):
     return o, lse
 
 
-def _backward(entry, q, k, v, lens, o, lse, do, mask_args, sm_scale, d_lse):
+def _backward(entry, q, k, v, lens, o, lse, do, mask_args, sm_scale, d_lse, flags=0):
     from .chill import _BWD_PATHS, _backward_operand
 
     lib, functor_id = entry
     do = _backward_operand(do)
     deterministic = _cabi.is_deterministic()
     key = ("b", id(lib), functor_id, mask_args, q.shape, q.stride(), k.shape, k.stride(), v.stride(), o.stride(),
-           do.stride(), lse.stride(), q.dtype, sm_scale, lens is None, deterministic,
+           do.stride(), lse.stride(), q.dtype, sm_scale, lens is None, deterministic, flags,
            None if d_lse is None else d_lse.stride())
     cache = _cache()
     ent = cache.get(key)
@@ -117,7 +117,7 @@ def _backward(entry, q, k, v, lens, o, lse, do, mask_args, sm_scale, d_lse):
     dk = torch.empty(k.shape, dtype=k.dtype, device=dev)
     dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
     if ent is None:
-        shape = _cabi.make_shape(q, k, functor_id, mask_args, None, sm_scale)
+        shape = _cabi.make_shape(q, k, functor_id, mask_args, None, sm_scale, flags=flags)
         a = _cabi.backward_args(q, k, v, o, do, lse, delta, dq, dk, dv, shape, None, d_lse)
         tc = lib.chill_bwd_uses_tensor_cores(C.byref(a)) == 1
         nacc = lib.chill_bwd_dq_accum_bytes(C.byref(a.s)) if (tc and not deterministic) else 0
@@ -149,7 +149,7 @@ class _ChillAttentionEager(torch.autograd.Function):
         q, k, v = _pack(q, k, v)  # the packed copies are what the backward reads again
         o, lse = _forward(entry, q, k, v, lens, mask_args, sm_scale, True, flags)
         ctx.save_for_backward(q, k, v, o, lse, lens)
-        ctx.entry, ctx.mask_args, ctx.sm_scale = entry, mask_args, sm_scale
+        ctx.entry, ctx.mask_args, ctx.sm_scale, ctx.flags = entry, mask_args, sm_scale, flags
         ctx.set_materialize_grads(False)
         if not return_lse:
             ctx.mark_non_differentiable(lse)
@@ -163,9 +163,9 @@ class _ChillAttentionEager(torch.autograd.Function):
         d_lse = dlse.float() if dlse is not None else None  # a gradient that reached the returned LSE is propagated
         if q.device.index != torch._C._cuda_getDevice():
             with torch.cuda.device(q.device):
-                dq, dk, dv = _backward(ctx.entry, q, k, v, lens, o, lse, do, ctx.mask_args, ctx.sm_scale, d_lse)
+                dq, dk, dv = _backward(ctx.entry, q, k, v, lens, o, lse, do, ctx.mask_args, ctx.sm_scale, d_lse, ctx.flags)
         else:
-            dq, dk, dv = _backward(ctx.entry, q, k, v, lens, o, lse, do, ctx.mask_args, ctx.sm_scale, d_lse)
+            dq, dk, dv = _backward(ctx.entry, q, k, v, lens, o, lse, do, ctx.mask_args, ctx.sm_scale, d_lse, ctx.flags)
         return dq, dk, dv, None, None, None, None, None, None
 
 

@@ -15,7 +15,7 @@ the current CUDA stream.  ``autotune`` and ``prescale_qk`` are accepted for
 compatibility and have no effect: there is nothing to tune at run time and the
 softmax scale is always applied in fp32 inside the exponent.
 ``precision`` only matters for fp32 inputs: "ieee" (default) computes them with IEEE fp32 FMAs, "tf32" lets the
-forward (head dim 64 / 128) run on the tensor cores in TF32; the backward of fp32 inputs is IEEE fp32 either way.
+forward (head dim 64 / 128) and the backward (head dim 64) run on the tensor cores in TF32.
 """
 from __future__ import annotations
 
@@ -57,7 +57,12 @@ def _tensor_core_operands(q, k, v):
     return tuple(t if _cabi.tma_compatible(t) else t.contiguous() for t in (q, k, v))
 
 
-def _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scale, d_lse=None):
+def _precision_flags(precision, dtype) -> int:
+    """precision="tf32" (the reference's tl.dot input_precision) lets fp32 tensors use the TF32 tensor cores."""
+    return _cabi.FLAG_ALLOW_TF32 if (precision == "tf32" and dtype == torch.float32) else 0
+
+
+def _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scale, d_lse=None, flags=0):
     import ctypes as C
 
     q, k, v = _tensor_core_operands(q, k, v)
@@ -68,7 +73,7 @@ def _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scal
         DK = torch.empty_like(k, memory_format=torch.contiguous_format)
         DV = torch.empty_like(v, memory_format=torch.contiguous_format)
         lens_c = lens.contiguous() if lens is not None else None
-        shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale)
+        shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale, flags=flags)
         a = _cabi.backward_args(q, k, v, o, do, lse, delta, DQ, DK, DV, shape, None, d_lse)
         tc = lib.chill_bwd_uses_tensor_cores(C.byref(a)) == 1
         _BWD_PATHS["tensor_core" if tc else "generic"] += 1
@@ -140,8 +145,7 @@ def register_chill_mask(mask: ChillMask):
             O = torch.empty_like(q, memory_format=torch.contiguous_format)
             LSE = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if return_lse else None
             lens_c = lens.contiguous() if lens is not None else None
-            # precision="tf32" (the reference's tl.dot input_precision): fp32 tensors may use the TF32 tensor cores
-            flags = _cabi.FLAG_ALLOW_TF32 if (precision == "tf32" and q.dtype == torch.float32) else 0
+            flags = _precision_flags(precision, q.dtype)
             shape = _cabi.make_shape(q, k, functor_id, mask_args, lens_c, sm_scale, flags=flags)
             _cabi.forward(lib, q, k, v, O, LSE, shape)
         if LSE is None:
@@ -171,7 +175,8 @@ def register_chill_mask(mask: ChillMask):
         precision: str,
         autotune: bool,
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        return _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scale)
+        return _run_backward(lib, functor_id, q, k, v, lens, o, lse, do, mask_args, sm_scale,
+                             flags=_precision_flags(precision, q.dtype))
 
     @torch.library.register_fake(f"chill_attention::backward{mask_name}")
     def attention_backward_adapter_abstract(q, k, v, lens, o, lse, do, mask_args, sm_scale, prescale_qk, precision,
@@ -295,8 +300,8 @@ def chill_attention(
         sm_scale: softmax scale, default head_dim ** -0.5.
         return_lse: also return the log-sum-exp of every row in log2 units, shape [batch, heads, seq_len].
         prescale_qk, autotune: accepted for compatibility with the reference, no effect.
-        precision: "ieee" or "tf32"; for fp32 inputs "tf32" runs the forward on the tensor cores in TF32
-            (head dim 64 / 128, ~1e-3 output error instead of ~1e-6), everything else is IEEE fp32.
+        precision: "ieee" or "tf32"; for fp32 inputs "tf32" runs the forward (head dim 64 / 128) and the backward
+            (head dim 64) on the tensor cores in TF32 (~1e-3 error instead of ~1e-6), everything else is IEEE fp32.
 
     Returns: O, or (O, LSE) when ``return_lse``.
     """
@@ -309,7 +314,7 @@ def chill_attention(
     compiling = torch.compiler.is_compiling()
     if not compiling and entry is not None and _eager.usable(q, k, v, lens):
         # plain eager call: same kernels through the short host path (see _eager.py), which validates the arguments
-        flags = _cabi.FLAG_ALLOW_TF32 if (precision == "tf32" and q.dtype == torch.float32) else 0
+        flags = _precision_flags(precision, q.dtype)
         return _eager.attention(entry, q, k, v, lens, mask.constargs, float(sm_scale), bool(return_lse), flags)
     if not compiling:
         for i in (q, k, v):

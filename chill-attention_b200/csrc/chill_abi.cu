@@ -298,6 +298,19 @@ static PartOut to_part(const chill_bwd_args& a) {
   return o;
 }
 
+// fp32 tensors whose caller allowed TF32, head dim 64: backward on the tensor cores (bwd_tf32.cuh).  dQ / dK / dV
+// are written by the threads themselves, 16 bytes at a time.
+static bool bwd_tf32_eligible(const chill_bwd_args& a) {
+  const chill_shape& s = a.s;
+  if (s.flags & CHILL_FLAG_FORCE_GENERIC) return false;
+  if (s.dtype != CHILL_F32 || !(s.flags & CHILL_FLAG_ALLOW_TF32) || s.D != 64 || !(s.sm_scale > 0.f)) return false;
+  if (a.dk_part != nullptr) return false;
+  return tma_ok(a.q, a.q_strides, s.B, s.H, s.Lq, 4) && tma_ok(a.k, a.k_strides, s.B, s.H_kv, s.Lk, 4) &&
+         tma_ok(a.v, a.v_strides, s.B, s.H_kv, s.Lk, 4) && tma_ok(a.d_o, a.do_strides, s.B, s.H, s.Lq, 4) &&
+         tma_ok(a.dq, a.dq_strides, s.B, s.H, s.Lq, 4) && tma_ok(a.dk, a.dk_strides, s.B, s.H_kv, s.Lk, 4) &&
+         tma_ok(a.dv, a.dv_strides, s.B, s.H_kv, s.Lk, 4) && a.lse_strides[2] == 1;
+}
+
 static BwdP to_bwdp(const chill_bwd_args& a) {
   BwdP p;
   p.g = to_geo(a.s);
@@ -388,6 +401,43 @@ static SideStream* side_stream() {
   return &s;
 }
 
+static void fill_bwd_tc_params(const chill_bwd_args& a, tc::BwdTcParams& p) {
+  const chill_shape& s = a.s;
+  p.g = to_geo(s);
+  p.lse = a.lse;
+  p.lse_sb = a.lse_strides[0]; p.lse_sh = a.lse_strides[1]; p.lse_sl = a.lse_strides[2];
+  p.delta = a.delta;
+  p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
+  p.dq_sb = a.dq_strides[0]; p.dq_sh = a.dq_strides[1]; p.dq_sl = a.dq_strides[2];
+  p.dk_sb = a.dk_strides[0]; p.dk_sh = a.dk_strides[1]; p.dk_sl = a.dk_strides[2];
+  p.dv_sb = a.dv_strides[0]; p.dv_sh = a.dv_strides[1]; p.dv_sl = a.dv_strides[2];
+  p.which = bwd_which(s.flags);
+  p.dq_accum = nullptr;
+  p.part = to_part(a);
+}
+
+static int bwd_tf32(const chill_bwd_args& a, cudaStream_t st) {
+  const chill_shape& s = a.s;
+  CUtensorMap maps[7];
+  const void* ptrs[7] = {a.q, a.q, a.k, a.k, a.v, a.d_o, a.d_o};
+  const int64_t* strs[7] = {a.q_strides, a.q_strides, a.k_strides, a.k_strides, a.v_strides, a.do_strides, a.do_strides};
+  const bool is_kv[7] = {false, false, true, true, true, false, false};
+  const bool atoms32[7] = {false, true, false, true, false, false, true};  // the copies that are read MN-major
+  for (int i = 0; i < 7; ++i) {
+    int rc = make_map(&maps[i], ptrs[i], strs[i], s.B, is_kv[i] ? s.H_kv : s.H, is_kv[i] ? s.Lk : s.Lq, s.D, s.dtype,
+                      tc::kTile, atoms32[i] ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != CHILL_OK) return rc;
+  }
+  tc::BwdTcParams p;
+  fill_bwd_tc_params(a, p);
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
+  int e = 0;
+  CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd_tf32<MaskT>(maps, p, st)))
+  if (e == 0) g_launches += (p.which == 3 ? 2 : 1);
+  return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tf32 launch");
+}
+
 static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = true, bool fused = true) {
   const chill_shape& s = a.s;
   CUtensorMap maps[7];
@@ -400,19 +450,9 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = tr
     if (rc != CHILL_OK) return rc;
   }
   tc::BwdTcParams p;
-  p.g = to_geo(s);
-  p.lse = a.lse;
-  p.lse_sb = a.lse_strides[0]; p.lse_sh = a.lse_strides[1]; p.lse_sl = a.lse_strides[2];
-  p.delta = a.delta;
-  p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
-  p.dq_sb = a.dq_strides[0]; p.dq_sh = a.dq_strides[1]; p.dq_sl = a.dq_strides[2];
-  p.dk_sb = a.dk_strides[0]; p.dk_sh = a.dk_strides[1]; p.dk_sl = a.dk_strides[2];
-  p.dv_sb = a.dv_strides[0]; p.dv_sh = a.dv_strides[1]; p.dv_sl = a.dv_strides[2];
+  fill_bwd_tc_params(a, p);
   p.status = device_status_ptr();
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
-  p.which = bwd_which(s.flags);
-  p.dq_accum = nullptr;
-  p.part = to_part(a);
   int e = 0;
   if (fused && p.which == 3 && a.dq_accum != nullptr) {
     if ((reinterpret_cast<uintptr_t>(a.dq_accum) & 15u) != 0) return CHILL_E_INVALID;
@@ -540,7 +580,7 @@ int chill_fwd_uses_tensor_cores(const chill_fwd_args* a) {
 int chill_bwd_uses_tensor_cores(const chill_bwd_args* a) {
   int st = check_bwd(a, true);
   if (st != CHILL_OK) return st;
-  return bwd_tc_eligible(*a) ? 1 : 0;
+  return (bwd_tc_eligible(*a) || bwd_tf32_eligible(*a)) ? 1 : 0;
 }
 
 int chill_fwd(const chill_fwd_args* a, void* stream) {
@@ -572,6 +612,7 @@ int chill_bwd(const chill_bwd_args* a, void* stream) {
   int st = check_bwd(a, true);
   if (st != CHILL_OK) return st;
   if (bwd_tc_eligible(*a)) return bwd_tc(*a, (cudaStream_t)stream);
+  if (bwd_tf32_eligible(*a)) return bwd_tf32(*a, (cudaStream_t)stream);
   if (a->s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
   return bwd_generic(*a, (cudaStream_t)stream);
 }
@@ -595,6 +636,7 @@ int chill_bwd_noalloc(const chill_bwd_args* a, void* stream) {
   st = delta_launch(b, (cudaStream_t)stream);
   if (st != CHILL_OK) return st;
   if (bwd_tc_eligible(b)) return bwd_tc(b, (cudaStream_t)stream, /*concurrent=*/false, /*fused=*/false);  // one stream, no helper objects
+  if (bwd_tf32_eligible(b)) return bwd_tf32(b, (cudaStream_t)stream);
   if (b.s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
   return bwd_generic(b, (cudaStream_t)stream);
 }

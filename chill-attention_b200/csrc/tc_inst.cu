@@ -2,6 +2,7 @@
 //   -DCHILL_INST_MASK=<functor struct>   (e.g. CausalMask)
 #include "bwd_fused.cuh"
 #include "bwd_tc.cuh"
+#include "bwd_tf32.cuh"
 #include "fwd_tc.cuh"
 #include "fwd_tf32.cuh"
 #include "tc_launch.h"
@@ -59,6 +60,11 @@ int tc_launch_fwd_tf32<InstMask>(int D, const CUtensorMap* maps, const tc::FwdTc
   if (D == 64) return launch_fwd_tf32_one<64>(maps, p, grid, st);
   if (D == 128) return launch_fwd_tf32_one<128>(maps, p, grid, st);
   return (int)cudaErrorInvalidValue;
+}
+
+template <>
+int tc_launch_bwd_tf32<InstMask>(const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st) {
+  return tc::launch_bwd_tf32<InstMask>(maps, p, st);
 }
 
 template <>

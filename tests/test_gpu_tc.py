@@ -292,6 +292,57 @@ def test_fp32_forward_in_tf32_with_lens_and_ragged_length(_lib):
         assert ((lse.cpu().double() - lse_ref)[fin].abs() / lse_ref[fin].abs().clamp(min=1.0)).max().item() <= 3e-3
 
 
+@pytest.mark.parametrize("mask", big_masks(), ids=str)
+@pytest.mark.parametrize("L", [128, 700])
+def test_fp32_backward_in_tf32_head_dim_64(mask, L, _lib):
+    """precision="tf32" also puts the backward of fp32 tensors on the tensor cores for head dim 64
+    (csrc/bwd_tf32.cuh).  Stated bars against the fp64 oracle on N(0,1) inputs: gradients 5e-3 relative
+    (Frobenius), padded rows exactly zero; GQA and per-row lengths included."""
+    import chill_attention as ca
+    from chill_attention import chill as chill_mod
+    from chill_attention import chill_attention
+
+    q, k, v, do = make_inputs(3, 4, 2, L, 64, torch.float32, seed=53)
+    lens = torch.tensor([L, max(1, L // 3), L + 1], dtype=torch.int32)
+    g_ref = oracle_all(mask, q, k, v, do, lens)[2:]
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    before = chill_mod.backward_path_counts()
+    o = chill_attention(qd, kd, vd, mask=mask, lens=lens.cuda(), precision="tf32")
+    o.backward(do.cuda())
+    after = chill_mod.backward_path_counts()
+    assert after["tensor_core"] == before["tensor_core"] + 1 and after["generic"] == before["generic"]
+    valid = torch.arange(L)[None, None, :] < lens.long()[:, None, None]
+    for name, got, ref in zip(("dq", "dk", "dv"), (qd.grad, kd.grad, vd.grad), g_ref):
+        got = got.cpu().double()
+        assert torch.isfinite(got).all(), name
+        rel = ((got - ref).norm() / ref.norm()).item()
+        assert rel <= 5e-3, f"{name}: {rel}"
+        pad = (~valid).expand(3, got.shape[1], L)
+        assert (got[pad] == 0).all(), f"{name}: rows at or beyond lens[b] carry exactly zero gradient"
+    # the same call twice: bitwise equal (no atomics in these kernels)
+    q2, k2, v2 = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    chill_attention(q2, k2, v2, mask=mask, lens=lens.cuda(), precision="tf32").backward(do.cuda())
+    for a, b in zip((qd.grad, kd.grad, vd.grad), (q2.grad, k2.grad, v2.grad)):
+        assert torch.equal(a, b)
+
+
+def test_fp32_tf32_backward_of_head_dim_128_stays_ieee(_lib):
+    """Head dim 128 in fp32 does not fit the TF32 backward's shared-memory plan: IEEE kernels, same bars."""
+    import chill_attention as ca
+    from chill_attention import chill as chill_mod
+    from chill_attention import chill_attention
+
+    mask = ca.CausalChillMask()
+    q, k, v, do = make_inputs(1, 2, 2, 200, 128, torch.float32, seed=54)
+    g_ref = oracle_all(mask, q, k, v, do)[2:]
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    before = chill_mod.backward_path_counts()
+    chill_attention(qd, kd, vd, mask=mask, precision="tf32").backward(do.cuda())
+    assert chill_mod.backward_path_counts()["generic"] == before["generic"] + 1
+    for got, ref in zip((qd.grad, kd.grad, vd.grad), g_ref):
+        assert ((got.cpu().double() - ref).norm() / ref.norm()).item() <= 5e-3
+
+
 def test_a_bounded_wait_that_runs_out_ends_as_a_status_code(_lib):
     """The give-up path of the kernels' bounded mbarrier waits, exercised without faulting or hanging anything:
     a small kernel whose roles all wait (1 ms limit) on a barrier nobody arrives at must return, release its
