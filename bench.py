@@ -81,9 +81,9 @@ WORKLOADS = {
     "c2s": ("CausalChillMask", (), "bfloat16", 2, 16, 4096, 128),
     # c3 with a quarter of the batch, for the same purpose (head dim 64: 64-key tiles, four CTAs per SM)
     "c3s": ("ChunkwiseChillMask", (128, 2), "float16", 1, 32, 16384, 64),
-    # fp32 tensors with precision="tf32": forward on the TF32 tensor cores, backward in IEEE fp32 on the generic
-    # kernels (seconds per step: use --steps 2); the forward figure is the one of interest
+    # fp32 tensors with precision="tf32": forward and backward on the TF32 tensor cores (two-kernel backward)
     "c2f32": ("CausalChillMask", (), "float32", 2, 16, 4096, 128),
+    "c2f32d64": ("CausalChillMask", (), "float32", 2, 32, 4096, 64),
 }
 
 

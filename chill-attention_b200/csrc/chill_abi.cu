@@ -298,12 +298,12 @@ static PartOut to_part(const chill_bwd_args& a) {
   return o;
 }
 
-// fp32 tensors whose caller allowed TF32, head dim 64: backward on the tensor cores (bwd_tf32.cuh).  dQ / dK / dV
+// fp32 tensors whose caller allowed TF32, head dim 64 / 128: backward on the tensor cores (bwd_tf32.cuh).  dQ / dK / dV
 // are written by the threads themselves, 16 bytes at a time.
 static bool bwd_tf32_eligible(const chill_bwd_args& a) {
   const chill_shape& s = a.s;
   if (s.flags & CHILL_FLAG_FORCE_GENERIC) return false;
-  if (s.dtype != CHILL_F32 || !(s.flags & CHILL_FLAG_ALLOW_TF32) || s.D != 64 || !(s.sm_scale > 0.f)) return false;
+  if (s.dtype != CHILL_F32 || !(s.flags & CHILL_FLAG_ALLOW_TF32) || (s.D != 64 && s.D != 128) || !(s.sm_scale > 0.f)) return false;
   if (a.dk_part != nullptr) return false;
   return tma_ok(a.q, a.q_strides, s.B, s.H, s.Lq, 4) && tma_ok(a.k, a.k_strides, s.B, s.H_kv, s.Lk, 4) &&
          tma_ok(a.v, a.v_strides, s.B, s.H_kv, s.Lk, 4) && tma_ok(a.d_o, a.do_strides, s.B, s.H, s.Lq, 4) &&
@@ -418,14 +418,21 @@ static void fill_bwd_tc_params(const chill_bwd_args& a, tc::BwdTcParams& p) {
 
 static int bwd_tf32(const chill_bwd_args& a, cudaStream_t st) {
   const chill_shape& s = a.s;
-  CUtensorMap maps[7];
-  const void* ptrs[7] = {a.q, a.q, a.k, a.k, a.v, a.d_o, a.d_o};
-  const int64_t* strs[7] = {a.q_strides, a.q_strides, a.k_strides, a.k_strides, a.v_strides, a.do_strides, a.do_strides};
-  const bool is_kv[7] = {false, false, true, true, true, false, false};
-  const bool atoms32[7] = {false, true, false, true, false, false, true};  // the copies that are read MN-major
-  for (int i = 0; i < 7; ++i) {
-    int rc = make_map(&maps[i], ptrs[i], strs[i], s.B, is_kv[i] ? s.H_kv : s.H, is_kv[i] ? s.Lk : s.Lq, s.D, s.dtype,
-                      tc::kTile, atoms32[i] ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
+  // streamed tiles have TO rows (128 at head dim 64, 32 at head dim 128), resident ones 128; "mn" copies (read
+  // MN-major by the tensor core) take the 128-byte swizzle with 32-byte atoms
+  const int to = s.D == 64 ? 128 : 32;
+  struct MapSpec { const void* p; const int64_t* st; bool kv; int rows; bool mn; };
+  const MapSpec spec[11] = {
+      {a.q, a.q_strides, false, to, false},   {a.q, a.q_strides, false, to, true},
+      {a.d_o, a.do_strides, false, to, false}, {a.d_o, a.do_strides, false, to, true},
+      {a.k, a.k_strides, true, tc::kTile, false}, {a.v, a.v_strides, true, tc::kTile, false},
+      {a.q, a.q_strides, false, tc::kTile, false}, {a.d_o, a.do_strides, false, tc::kTile, false},
+      {a.k, a.k_strides, true, to, false},    {a.k, a.k_strides, true, to, true},
+      {a.v, a.v_strides, true, to, false}};
+  CUtensorMap maps[11];
+  for (int i = 0; i < 11; ++i) {
+    int rc = make_map(&maps[i], spec[i].p, spec[i].st, s.B, spec[i].kv ? s.H_kv : s.H, spec[i].kv ? s.Lk : s.Lq, s.D, s.dtype,
+                      spec[i].rows, spec[i].mn ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != CHILL_OK) return rc;
   }
   tc::BwdTcParams p;
@@ -433,7 +440,7 @@ static int bwd_tf32(const chill_bwd_args& a, cudaStream_t st) {
   p.status = device_status_ptr();
   if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
   int e = 0;
-  CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd_tf32<MaskT>(maps, p, st)))
+  CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd_tf32<MaskT>(s.D, maps, p, st)))
   if (e == 0) g_launches += (p.which == 3 ? 2 : 1);
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tf32 launch");
 }

@@ -63,8 +63,8 @@ int tc_launch_fwd_tf32<InstMask>(int D, const CUtensorMap* maps, const tc::FwdTc
 }
 
 template <>
-int tc_launch_bwd_tf32<InstMask>(const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st) {
-  return tc::launch_bwd_tf32<InstMask>(maps, p, st);
+int tc_launch_bwd_tf32<InstMask>(int D, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st) {
+  return tc::launch_bwd_tf32<InstMask>(D, maps, p, st);
 }
 
 template <>

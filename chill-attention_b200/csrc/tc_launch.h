@@ -49,9 +49,8 @@ int tc_launch_fwd_tf32(int D, const CUtensorMap* maps, const tc::FwdTcParams& p,
 template <class M>
 int tc_launch_bwd(int dtype, int D, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st);
 
-// fp32 tensors in TF32, head dim 64 (bwd_tf32.cuh); maps: Q, Q (32-byte atoms), K, K (32-byte atoms), V, dO,
-// dO (32-byte atoms).
+// fp32 tensors in TF32, head dim 64 / 128 (bwd_tf32.cuh, which lists the eleven maps).
 template <class M>
-int tc_launch_bwd_tf32(const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st);
+int tc_launch_bwd_tf32(int D, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st);
 
 }  // namespace chill

@@ -294,15 +294,16 @@ def test_fp32_forward_in_tf32_with_lens_and_ragged_length(_lib):
 
 @pytest.mark.parametrize("mask", big_masks(), ids=str)
 @pytest.mark.parametrize("L", [128, 700])
-def test_fp32_backward_in_tf32_head_dim_64(mask, L, _lib):
-    """precision="tf32" also puts the backward of fp32 tensors on the tensor cores for head dim 64
-    (csrc/bwd_tf32.cuh).  Stated bars against the fp64 oracle on N(0,1) inputs: gradients 5e-3 relative
-    (Frobenius), padded rows exactly zero; GQA and per-row lengths included."""
+@pytest.mark.parametrize("D", [64, 128])
+def test_fp32_backward_in_tf32(mask, L, D, _lib):
+    """precision="tf32" also puts the backward of fp32 tensors on the tensor cores (csrc/bwd_tf32.cuh; head dim
+    64 streams tiles of 128 positions, head dim 128 tiles of 32).  Stated bars against the fp64 oracle on N(0,1)
+    inputs: gradients 5e-3 relative (Frobenius), padded rows exactly zero; GQA and per-row lengths included."""
     import chill_attention as ca
     from chill_attention import chill as chill_mod
     from chill_attention import chill_attention
 
-    q, k, v, do = make_inputs(3, 4, 2, L, 64, torch.float32, seed=53)
+    q, k, v, do = make_inputs(3, 4, 2, L, D, torch.float32, seed=53)
     lens = torch.tensor([L, max(1, L // 3), L + 1], dtype=torch.int32)
     g_ref = oracle_all(mask, q, k, v, do, lens)[2:]
     qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
@@ -326,21 +327,20 @@ def test_fp32_backward_in_tf32_head_dim_64(mask, L, _lib):
         assert torch.equal(a, b)
 
 
-def test_fp32_tf32_backward_of_head_dim_128_stays_ieee(_lib):
-    """Head dim 128 in fp32 does not fit the TF32 backward's shared-memory plan: IEEE kernels, same bars."""
+def test_fp32_without_the_tf32_flag_stays_ieee(_lib):
+    """precision="ieee" (the default) never touches the TF32 kernels: fp32 bars of the generic kernels."""
     import chill_attention as ca
     from chill_attention import chill as chill_mod
     from chill_attention import chill_attention
 
     mask = ca.CausalChillMask()
-    q, k, v, do = make_inputs(1, 2, 2, 200, 128, torch.float32, seed=54)
+    q, k, v, do = make_inputs(1, 2, 2, 200, 64, torch.float32, seed=54)
     g_ref = oracle_all(mask, q, k, v, do)[2:]
     qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
     before = chill_mod.backward_path_counts()
-    chill_attention(qd, kd, vd, mask=mask, precision="tf32").backward(do.cuda())
+    chill_attention(qd, kd, vd, mask=mask).backward(do.cuda())
     assert chill_mod.backward_path_counts()["generic"] == before["generic"] + 1
-    for got, ref in zip((qd.grad, kd.grad, vd.grad), g_ref):
-        assert ((got.cpu().double() - ref).norm() / ref.norm()).item() <= 5e-3
+    check_grads((qd.grad, kd.grad, vd.grad), g_ref, torch.float32)
 
 
 def test_a_bounded_wait_that_runs_out_ends_as_a_status_code(_lib):
