@@ -34,10 +34,10 @@ def attention_fwd_bwd_host(q, k, v, do, mask: ChillMask, sm_scale=None, out=None
     (pinned; pass ``out=(o, dq, dk, dv)`` to reuse buffers).  Synchronises before returning.
 
     The batch goes through the GPU in chunks of `chunk_batches` batch rows x `chunk_heads` heads (default: up to
-    80 MB of input per chunk, whole GQA groups).  The first chunk's upload and the last chunk's download are the
+    40 MB of input per chunk, whole GQA groups).  The first chunk's upload and the last chunk's download are the
     only transfers that nothing overlaps, which favours small chunks, but every chunk costs ~0.3 ms of host time
-    (copies, events, launches): measured on C2 (67 MB per batch row), 8 chunks of 67 MB reach 148-155 TFLOP/s,
-    32 chunks of 17 MB 124, 64 chunks of 8 MB 76."""
+    (copies, events, launches): measured on C2 (67 MB per batch row) in one session, 8 chunks of 67 MB reach
+    144 TFLOP/s, 16 chunks of 34 MB 153, 32 chunks of 17 MB 141."""
     device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     B, H, L, D = q.shape
     Hkv = k.shape[1]
@@ -50,7 +50,7 @@ def attention_fwd_bwd_host(q, k, v, do, mask: ChillMask, sm_scale=None, out=None
     cb = max(1, min(chunk_batches, B))
     G = H // Hkv
     if chunk_heads is None:
-        target = float(os.environ.get("CHILL_HOST_CHUNK_MB", "80")) * 1e6
+        target = float(os.environ.get("CHILL_HOST_CHUNK_MB", "40")) * 1e6
         bytes_per_head = cb * L * D * q.element_size() * (2 + 2.0 / G)
         chunk_heads = _heads_per_chunk(H, G, bytes_per_head, target)
     ch = max(G, min(H, (chunk_heads // G) * G))
