@@ -77,10 +77,10 @@ extern "C" {
 #define CHILL_FLAG_BWD_ONLY_DQ 8u   /* chill_bwd launches only the dQ kernel */
 #define CHILL_FLAG_ALLOW_TF32 16u   /* fp32 tensors may go through the tensor cores in TF32 (10-bit mantissa):
                                      * chill_fwd then runs its tcgen05 kernel for head dim 64 / 128 and chill_bwd its
-                                     * TF32 kernels for head dim 64; the reference's precision="tf32"
+                                     * TF32 kernels for head dim 64 / 128; the reference's precision="tf32"
                                      * (chill_fwd.py:13-359, chill_bwd_dq.py:312, chill_bwd_dkdv.py:347:
-                                     * input_precision).  Without the flag, and for the backward of head dim 128,
-                                     * fp32 is computed in IEEE fp32 by the generic kernels. */
+                                     * input_precision).  Without the flag, and for other head dims, fp32 is
+                                     * computed in IEEE fp32 by the generic kernels. */
 
 /* The mask constants a ChillMask instance was built with (ChillMask.constargs,
  * mask.py:31-49).  Each is passed both ways: `i[n]` = the value truncated to an
