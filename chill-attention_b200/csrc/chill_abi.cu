@@ -233,8 +233,10 @@ static int fwd_tc(const chill_fwd_args& a, cudaStream_t st) {
   if ((rc = make_map(&maps[0], a.q, a.q_strides, s.B, s.H, s.Lq, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
   // V is the MN-major operand of O += P V; with 32-bit elements that takes the 128B swizzle with 32-byte atoms
   const bool tf32 = s.dtype == CHILL_F32;
-  // keys per K / V tile of the kernel that will run (16-bit head dim 64: 64-key tiles, see FwdShape)
-  const int kv_rows = (!tf32 && s.D == 64) ? tc::FwdShape<64>::kKeys : tc::kTile;
+  // keys per K / V tile of the kernel that will run (see FwdShape)
+  const int kv_rows = tf32 ? tc::kTile
+                           : (s.D == 64 ? tc::FwdShape<64>::kKeys
+                                        : (s.D == 128 ? tc::FwdShape<128>::kKeys : tc::FwdShape<256>::kKeys));
   if ((rc = make_map(&maps[1], a.k, a.k_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, kv_rows)) != CHILL_OK) return rc;
   if ((rc = make_map(&maps[2], a.v, a.v_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, kv_rows,
                      tf32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B)) != CHILL_OK)

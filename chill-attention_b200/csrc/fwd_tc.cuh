@@ -61,15 +61,19 @@ constexpr int kTmemColsFwd = 256;
 // ~4100 clocks per 128-key tile per CTA against 1024 clocks of tensor work), so what counts is how many such chains an
 // SM runs side by side, which TMEM (512 columns: S + O per CTA) limits.  D = 128: S 128 + O 128 columns, two CTAs.
 // D = 64: key tiles of 64 keys need S 64 + O 64 = 128 columns, four CTAs; the narrower MMAs (N = 64) run at 2/3 of
-// the rate, which the kernel does not feel.  A CTA's register pool is threads x launch registers, and the softmax
+// the rate, which the kernel does not feel.  D = 128 spends its 256 columns on O and TWO 64-key S buffers instead:
+// S(j+1) = Q K(j+1)^T is issued before O += P(j) V(j), so it runs while the softmax warps work on tile j and the
+// chain of a CTA shrinks to softmax -> PV.  A CTA's register pool is threads x launch registers, and the softmax
 // warpgroup's setmaxnreg.inc is only ever granted if softmax + other <= 2 x launch.
 // D = 256: S 128 + O 256 columns and 192 KB of Q / K / V tiles leave room for one CTA per SM only.
 template <int D>
 struct FwdShape {
-  static constexpr int kKeys = (D == 64) ? 64 : 128;       // keys per tile
+  static constexpr int kKeys = (D <= 128) ? 64 : 128;      // keys per tile
+  static constexpr int kSBufs = (D == 128) ? 2 : 1;        // S / P buffers in TMEM
   static constexpr int kCtasPerSm = (D == 64) ? 4 : (D == 128 ? 2 : 1);
-  static constexpr int kStages = (D == 64) ? 2 : 1;        // K / V ring depth
-  static constexpr int kTmemCols = (kKeys + D <= 128) ? 128 : (kKeys + D <= 256 ? 256 : 512);
+  static constexpr int kStages = (D <= 128) ? 2 : 1;       // K / V ring depth
+  static constexpr int kSO = kSBufs * kKeys + D;           // columns in use: S buffers, then O
+  static constexpr int kTmemCols = (kSO <= 128) ? 128 : (kSO <= 256 ? 256 : 512);
   static constexpr int kLaunchRegs = (65536 / (kCtasPerSm * kFwdThreads) > 128) ? 128 : 65536 / (kCtasPerSm * kFwdThreads);
   static constexpr int kSoftmaxRegs = (D == 64) ? 96 : 200;
   static constexpr int kOtherRegs = (D == 64) ? 32 : 56;
@@ -95,7 +99,7 @@ struct FwdSmem {
   static constexpr int kK = kQ + kTileBytes;
   static constexpr int kV = kK + NSTAGE * kKvBytes;
   static constexpr int kBars = kV + NSTAGE * kKvBytes;
-  static constexpr int kNumBars = 4 + 4 * NSTAGE;
+  static constexpr int kNumBars = 8 + 4 * NSTAGE;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
@@ -110,7 +114,8 @@ enum : int { kStProducer = 101, kStMma = 102, kStSoftmax = 103, kStEpilogue = 10
 template <typename T, int D, class M, int KT = kTile>
 __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_sel, bool first, bool full, int klim,
                                              int qg, int kg0, int n, const MaskArgs& margs, float c, float& m_used,
-                                             float& l) {
+                                             float& l, uint32_t bar_pv = 0, uint32_t pv_parity = 0,
+                                             const Guard* guard = nullptr) {
   // One pass over the row: all 128 scores of this thread's row come into registers, the maximum
   // is taken with 3-input max on four independent chains, and exponentials, row sum and the
   // 16-bit packing run on pairs (packed fp32 FMA / ADD).  Full tiles skip the mask arithmetic
@@ -148,6 +153,11 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   } else {
     const bool need = (m_cand - m_used) > kRescaleThreshold;  // false when both are -inf
     if (__any_sync(0xffffffffu, need)) {
+      // With two S buffers the previous tile's O += P V may still be running: wait for it before touching O.
+      if (bar_pv != 0) {
+        mbar_wait(bar_pv, pv_parity, *guard, kStSoftmax);
+        tc_fence_after();
+      }
       const float alpha = (m_cand == -CUDART_INF_F) ? 1.f : ex2(m_used - m_cand);
       l *= alpha;
       m_used = m_cand;
@@ -289,8 +299,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t sQ = base + L::kQ, sK = base + L::kK, sV = base + L::kV;
   const uint32_t bars = base + L::kBars;
-  const uint32_t bar_q_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_o_full = bars + 24;
-  const uint32_t bar_k_full = bars + 32, bar_k_empty = bar_k_full + 8 * NSTAGE, bar_v_full = bar_k_empty + 8 * NSTAGE,
+  constexpr int NSB = SH::kSBufs;
+  // s_full / p_full: one barrier per S buffer (bars + 8, + 16 / bars + 24, + 32); pv_done counts finished O += P V
+  const uint32_t bar_q_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 24, bar_o_full = bars + 40,
+                 bar_pv_done = bars + 48;
+  const uint32_t bar_k_full = bars + 64, bar_k_empty = bar_k_full + 8 * NSTAGE, bar_v_full = bar_k_empty + 8 * NSTAGE,
                  bar_v_empty = bar_v_full + 8 * NSTAGE;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
@@ -302,9 +315,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (lane == 0) {
       *abort_flag = 0;
       mbar_init(bar_q_full, 1);
-      mbar_init(bar_s_full, 1);
-      mbar_init(bar_p_full, 4);
+      for (int i = 0; i < NSB; ++i) {
+        mbar_init(bar_s_full + 8 * i, 1);
+        mbar_init(bar_p_full + 8 * i, 4);
+      }
       mbar_init(bar_o_full, 1);
+      mbar_init(bar_pv_done, 1);
       for (int s = 0; s < NSTAGE; ++s) {
         mbar_init(bar_k_full + 8 * s, 1);
         mbar_init(bar_k_empty + 8 * s, 1);
@@ -330,8 +346,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem;            // S / P columns
-  const uint32_t tO = tmem + KT;       // O columns
+  const uint32_t tS = tmem;            // S / P columns: NSB buffers of KT columns
+  const uint32_t tO = tmem + NSB * KT; // O columns
 
   if (warp == 4) {
     reg_dealloc<SH::kOtherRegs>();
@@ -368,31 +384,48 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       constexpr uint32_t hi_k = desc_hi_sw128(1024);  // both operand kinds: 8-row groups 1 KB apart
       const uint32_t q_lo = desc_lo_sw128(sQ, 16);
       bool ok = mbar_wait(bar_q_full, 0, guard, kStMma);
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      auto issue_s = [&](int j) -> bool {  // S(j) = Q K(j)^T into S buffer j % NSB: both K-major, 16 channels per MMA
         const int s = j % NSTAGE;
-        const uint32_t ph = (uint32_t)(j / NSTAGE) & 1u;
         const uint32_t k_lo = desc_lo_sw128(sK + s * L::kKvBytes, 16);
-        const uint32_t v_lo = desc_lo_sw128(sV + s * L::kKvBytes, kKvChunkBytes);  // MN-major: channel blocks one chunk apart
-        ok = mbar_wait(bar_k_full + 8 * s, ph, guard, kStMma);
-        if (!ok) break;
+        if (!mbar_wait(bar_k_full + 8 * s, (uint32_t)(j / NSTAGE) & 1u, guard, kStMma)) return false;
         tc_fence_after();
-        // S = Q K^T: both K-major; 16 channels (32 bytes) per instruction.
+        const uint32_t ts = tS + (uint32_t)((j % NSB) * KT);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)  // Q chunks are 128 rows apart, K chunks KT rows
-          mma_ss_lh(tS, q_lo + kmajor_step(kk), k_lo + (uint32_t)((kk / 4) * (kKvChunkBytes / 16) + (kk % 4) * 2), hi_k, idesc_s,
+          mma_ss_lh(ts, q_lo + kmajor_step(kk), k_lo + (uint32_t)((kk / 4) * (kKvChunkBytes / 16) + (kk % 4) * 2), hi_k, idesc_s,
                     kk > 0 ? 1u : 0u);
         mma_commit(bar_k_empty + 8 * s);
-        mma_commit(bar_s_full);
-        ok = mbar_wait(bar_p_full, (uint32_t)j & 1u, guard, kStMma);
-        if (!ok) break;
-        ok = mbar_wait(bar_v_full + 8 * s, ph, guard, kStMma);
-        if (!ok) break;
+        mma_commit(bar_s_full + 8 * (j % NSB));
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {  // O += P(j) V(j): P (16-bit) from TMEM, 16 keys = 8 columns per MMA
+        const int s = j % NSTAGE;
+        const uint32_t v_lo = desc_lo_sw128(sV + s * L::kKvBytes, kKvChunkBytes);  // MN-major: channel blocks one chunk apart
+        if (!mbar_wait(bar_p_full + 8 * (j % NSB), (uint32_t)(j / NSB) & 1u, guard, kStMma)) return false;
+        if (!mbar_wait(bar_v_full + 8 * s, (uint32_t)(j / NSTAGE) & 1u, guard, kStMma)) return false;
         tc_fence_after();
-        // O += P V: P (128 x 128, 16-bit) from TMEM, 16 keys = 8 columns and 2 KB of V per instruction.
+        const uint32_t tp = tS + (uint32_t)((j % NSB) * KT);
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk)
-          mma_ts_lh(tO, tS + kk * 8, v_lo + kk * 128, hi_k, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts_lh(tO, tp + kk * 8, v_lo + kk * 128, hi_k, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         mma_commit(bar_v_empty + 8 * s);
+        if (NSB > 1) mma_commit(bar_pv_done);
+        return true;
+      };
+      if (NSB == 1) {
+        // one S buffer: S(j+1) overwrites P(j), so the two GEMMs of a tile alternate
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          ok = issue_s(j);
+          if (ok) ok = issue_pv(j);
+        }
+      } else {
+        // S(j+1) goes to the other buffer and is issued ahead of O += P(j) V(j): it runs during softmax(j).
+        // MMAs execute in issue order, so S(j+2) cannot overtake the P V(j) that still reads its buffer.
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          if (j + 1 < n_tiles) ok = issue_s(j + 1);
+          if (ok) ok = issue_pv(j);
+        }
       }
       if (ok) mma_commit(bar_o_full);
     }
@@ -410,18 +443,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int j = 0; j < n_tiles; ++j) {
       const int kt = kt_lo + j;
       const int kg0 = kt * KT + g.k_off;
-      ok = mbar_wait(bar_s_full, (uint32_t)j & 1u, guard, kStSoftmax);
+      ok = mbar_wait(bar_s_full + 8 * (j % NSB), (uint32_t)(j / NSB) & 1u, guard, kStSoftmax);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
       const bool full = M::kHasKFullRange && kg0 >= full_lo && kg0 + KT <= full_hi && kg0 + KT <= n &&
                         kt * KT + KT <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * KT);  // columns >= klim do not exist
-      softmax_tile<T, D, M, KT>(tS, tO, lane_sel, j == 0, full, klim, qg, kg0, n, g.margs, c, m_used, l);
+      softmax_tile<T, D, M, KT>(tS + (uint32_t)((j % NSB) * KT), tO, lane_sel, j == 0, full, klim, qg, kg0, n, g.margs, c,
+                                m_used, l, NSB > 1 ? bar_pv_done : 0u, (uint32_t)(j - 1) & 1u, &guard);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full);  // one arrival per softmax warp
+      if (lane == 0) mbar_arrive(bar_p_full + 8 * (j % NSB));  // one arrival per softmax warp
     }
 
     // ---- epilogue: O / l -> 16-bit -> swizzled shared memory (Q's buffer) -> TMA store
