@@ -15,7 +15,7 @@ the current CUDA stream.  ``autotune`` and ``prescale_qk`` are accepted for
 compatibility and have no effect: there is nothing to tune at run time and the
 softmax scale is always applied in fp32 inside the exponent.
 ``precision`` only matters for fp32 inputs: "ieee" (default) computes them with IEEE fp32 FMAs, "tf32" lets the
-forward (head dim 64 / 128) and the backward (head dim 64) run on the tensor cores in TF32.
+forward and the backward (head dim 64 / 128) run on the tensor cores in TF32.
 """
 from __future__ import annotations
 
@@ -45,6 +45,11 @@ def _backward_operand(do: torch.Tensor) -> torch.Tensor:
     the call would otherwise be served by the ~1000x slower generic kernels.  One L x D copy fixes that (the
     reference asserts ``do.stride(-1) == 1`` at this point, chill.py:270)."""
     return do if _cabi.tma_compatible(do) else do.contiguous()
+
+
+#: 16-bit head dims that chill_attention() zero-pads to _PADDED_TO channels (tensor-core kernels instead of generic)
+_PADDED_HEAD_DIMS = (16, 32)
+_PADDED_TO = 64
 
 
 def _tensor_core_operands(q, k, v):
@@ -300,8 +305,12 @@ def chill_attention(
         sm_scale: softmax scale, default head_dim ** -0.5.
         return_lse: also return the log-sum-exp of every row in log2 units, shape [batch, heads, seq_len].
         prescale_qk, autotune: accepted for compatibility with the reference, no effect.
-        precision: "ieee" or "tf32"; for fp32 inputs "tf32" runs the forward (head dim 64 / 128) and the backward
-            (head dim 64) on the tensor cores in TF32 (~1e-3 error instead of ~1e-6), everything else is IEEE fp32.
+        precision: "ieee" or "tf32"; for fp32 inputs "tf32" runs forward and backward (head dim 64 / 128) on the
+            tensor cores in TF32 (~1e-3 error instead of ~1e-6), everything else is IEEE fp32.
+
+    fp16 / bf16 tensors with head dim 16 or 32 are zero-padded to 64 channels here, so that they run the tensor-core
+    kernels (zero channels change neither Q K^T nor the first head_dim columns of P V; autograd slices the gradients
+    back).  The reference serves these head dims with tl.dot directly (chill.py:81-92).
 
     Returns: O, or (O, LSE) when ``return_lse``.
     """
@@ -311,6 +320,18 @@ def chill_attention(
         entry = _REGISTRY.get(mask.name)
     if sm_scale is None:
         sm_scale = 1.0 / (q.shape[-1] ** 0.5)
+    head_dim = q.shape[-1]
+    if head_dim in _PADDED_HEAD_DIMS and q.dtype in (torch.float16, torch.bfloat16) and q.is_cuda \
+            and k.shape[-1] == head_dim and v.shape[-1] == head_dim and k.dtype == q.dtype and v.dtype == q.dtype:
+        pad = (0, _PADDED_TO - head_dim)
+        out = chill_attention(
+            torch.nn.functional.pad(q, pad), torch.nn.functional.pad(k, pad), torch.nn.functional.pad(v, pad), mask,
+            lens=lens, sm_scale=sm_scale, return_lse=return_lse, prescale_qk=prescale_qk, precision=precision,
+            autotune=autotune,
+        )
+        if return_lse:
+            return out[0][..., :head_dim].contiguous(), out[1]
+        return out[..., :head_dim].contiguous()
     compiling = torch.compiler.is_compiling()
     if not compiling and entry is not None and _eager.usable(q, k, v, lens):
         # plain eager call: same kernels through the short host path (see _eager.py), which validates the arguments

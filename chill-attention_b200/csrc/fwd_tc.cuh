@@ -1,20 +1,21 @@
-// Forward attention on tcgen05 tensor cores (sm_100a), 16-bit inputs, head dim 64 or 128.
+// Forward attention on tcgen05 tensor cores (sm_100a), 16-bit inputs, head dim 64, 128 or 256.
 //
-// One CTA owns a tile of 128 query rows of one (batch, head) and walks the key tiles (128 keys
-// each) that the mask functor's range function leaves for it.  Two CTAs share an SM, so one
-// CTA's softmax overlaps the other's MMAs.  Roles inside a CTA (192 threads):
+// One CTA owns a tile of 128 query rows of one (batch, head) and walks the key tiles (64 or 128 keys
+// each, see FwdShape) that the mask functor's range function leaves for it.  Several CTAs share an SM, so
+// one CTA's softmax overlaps the others' MMAs.  Roles inside a CTA:
 //
-//   warps 0-3  softmax: thread r owns query row r.  Per key tile: read S row from TMEM,
+//   warps 0-3  softmax: thread r owns query row r.  Per key tile: read the S row from TMEM,
 //              mask (boundary tiles only), online softmax in base 2, write P (16-bit) back
 //              into the TMEM columns S occupied, rescale the O accumulator in TMEM when the
 //              running max grew by more than 2^8, and finally normalise and store O / LSE.
 //   warp 4     TMA producer: Q once, then K and V tiles into shared-memory rings
-//              (128B-swizzled boxes of 64 channels x 128 rows); owns the TMEM allocation.
+//              (128B-swizzled boxes of 64 channels x KT rows); owns the TMEM allocation.
 //   warp 5     MMA issuer (one thread): S = Q K^T (both operands from shared memory) and
 //              O += P V (P from TMEM, V from shared memory, MN-major), completion signalled to
 //              mbarriers with tcgen05.commit.
 //
-// TMEM columns: [0,128) S (fp32), overlaid by P (16-bit, columns [0,64)); [128,128+D) O.
+// TMEM columns: kSBufs buffers of KT fp32 columns for S, each overlaid by its P (16-bit, first KT / 2
+// columns); then D columns of O.
 // Reference math: chill_attention/chill_fwd.py:188-359 (three-segment key loop, base-2
 // online softmax, LSE = m + log2 l); the segment split is replaced by a per-tile "full tile"
 // test derived from the functor's k_full_range_for_q.

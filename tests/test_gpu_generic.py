@@ -63,6 +63,51 @@ def test_odd_head_dims(mask, dtype, D):
     check_grads(grads, g_ref, dtype, lens)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=str)
+@pytest.mark.parametrize("D", [16, 32])
+def test_small_head_dims_take_the_tensor_cores(dtype, D):
+    """16-bit head dim 16 / 32 is zero-padded to 64 channels by chill_attention(): the tensor-core backward serves it,
+    the outputs have the caller's head dim and are contiguous, and a default sm_scale still means head_dim ** -0.5."""
+    import chill_attention as ca
+    from chill_attention.chill import backward_path_counts
+
+    mask = ca.SlidingWindowChillMask(40, 3)
+    q, k, v, do = make_inputs(2, 4, 2, 300, D, dtype)
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+    before = backward_path_counts()
+    o, lse, grads = run(mask, q, k, v, do)
+    after = backward_path_counts()
+    assert after["tensor_core"] == before["tensor_core"] + 1 and after["generic"] == before["generic"]
+    assert o.shape == q.shape and o.is_contiguous() and all(g.shape == q.shape or g.shape == k.shape for g in grads)
+    check_forward(o, lse, o_ref, lse_ref, None, dtype)
+    check_grads(grads, g_ref, dtype)
+
+
+@pytest.mark.parametrize("D", [16, 32])
+def test_small_head_dims_through_the_c_abi(D, _lib):
+    """A C-ABI caller that hands over 16-bit head dim 16 / 32 as it is gets the generic kernels: same results."""
+    import chill_attention as ca
+    from chill_attention import _cabi
+
+    mask = ca.ChunkwiseChillMask(16, 2)
+    dtype = torch.bfloat16
+    q, k, v, do = make_inputs(1, 4, 2, 150, D, dtype)
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o = torch.empty_like(qd)
+    lse = torch.empty(qd.shape[:3], dtype=torch.float32, device="cuda")
+    shape = _cabi.make_shape(qd, kd, _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor], mask.constargs, None, D ** -0.5)
+    _cabi.forward(_lib, qd, kd, vd, o, lse, shape)
+    delta = torch.empty_like(lse)
+    dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+    a = _cabi.backward_args(qd, kd, vd, o, dod, lse, delta, dq, dk, dv, shape)
+    assert _lib.chill_bwd_uses_tensor_cores(ctypes.byref(a)) == 0
+    _cabi.backward(_lib, qd, kd, vd, o, dod, lse, delta, dq, dk, dv, shape)
+    torch.cuda.synchronize()
+    check_forward(o, lse, o_ref, lse_ref, None, dtype)
+    check_grads((dq, dk, dv), g_ref, dtype)
+
+
 @pytest.mark.parametrize("mask", all_masks(), ids=str)
 @pytest.mark.parametrize("T", [1, 10, 16, 129])
 @pytest.mark.parametrize("heads", [(1, 1), (6, 1), (6, 3)])
