@@ -76,8 +76,8 @@ def build_library(out_path=None, custom_header=None, custom_functor=None, verbos
     obj_dir = os.path.join(os.path.dirname(out_path), "obj_" + os.path.basename(out_path))
     os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
-    jobs = [([nvcc] + NVCC_FLAGS + defines + ["-c", os.path.join(CSRC, "chill_abi.cu"), "-o",
-                                               os.path.join(obj_dir, "chill_abi.o")])]
+    jobs = [([nvcc] + NVCC_FLAGS + defines + ["-c", os.path.join(CSRC, src + ".cu"), "-o",
+                                               os.path.join(obj_dir, src + ".o")]) for src in ("chill_abi", "host_pipeline")]
     for fn in functors:
         jobs.append([nvcc] + NVCC_FLAGS + defines + [f"-DCHILL_INST_MASK={fn}", "-c", os.path.join(CSRC, "tc_inst.cu"),
                                                       "-o", os.path.join(obj_dir, f"tc_{fn}.o")])

@@ -32,7 +32,8 @@ BUILTIN_FUNCTOR_IDS = {
 
 _DTYPES = {torch.float32: CHILL_F32, torch.float16: CHILL_F16, torch.bfloat16: CHILL_BF16}
 
-ABI_VERSION = 4
+ABI_VERSION = 5
+FLAG_BWD_DETERMINISTIC = 32
 SELFTEST_STATUS = 901
 
 EXPORTS = (
@@ -41,6 +42,7 @@ EXPORTS = (
     "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_tabulate_blocks", "chill_mask_traits",
     "chill_read_device_status", "chill_selftest_bounded_wait",
     "chill_launch_count", "chill_abi_version", "chill_status_string", "chill_last_cuda_error",
+    "chill_host_workspace_bytes", "chill_fwd_bwd_host", "chill_host_chunk_schedule",
 )
 
 
@@ -74,6 +76,13 @@ class BwdArgs(C.Structure):
                 ("dv_strides", _S4), ("lse_strides", _S3), ("dq_accum", C.c_void_p), ("d_lse", C.c_void_p),
                 ("dlse_strides", _S3), ("dk_part", C.c_void_p), ("dv_part", C.c_void_p), ("part_strides", _S3),
                 ("part_head", C.c_int32), ("part_tail", C.c_int32)]
+
+
+class HostArgs(C.Structure):
+    _fields_ = [("s", Shape), ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("d_o", C.c_void_p),
+                ("o", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("chunk_groups", C.c_int32),
+                ("reserved", C.c_int32)]
 
 
 class ChillLibraryError(RuntimeError):
@@ -115,6 +124,12 @@ def load_library(path: str | None = None) -> C.CDLL:
         lib.chill_status_string.restype = C.c_char_p
         lib.chill_last_cuda_error.restype = C.c_char_p
         lib.chill_launch_count.restype = C.c_ulonglong
+        lib.chill_host_workspace_bytes.argtypes = [C.POINTER(HostArgs)]
+        lib.chill_host_workspace_bytes.restype = C.c_size_t
+        lib.chill_fwd_bwd_host.argtypes = [C.POINTER(HostArgs), C.c_void_p]
+        lib.chill_fwd_bwd_host.restype = C.c_int
+        lib.chill_host_chunk_schedule.argtypes = [C.POINTER(HostArgs), C.POINTER(C.c_int32), C.c_int32]
+        lib.chill_host_chunk_schedule.restype = C.c_int
         for name in ("chill_fwd", "chill_bwd_delta", "chill_bwd", "chill_bwd_noalloc", "chill_fwd_uses_tensor_cores",
                      "chill_bwd_uses_tensor_cores", "chill_mask_tabulate", "chill_mask_tabulate_blocks", "chill_mask_traits",
                      "chill_selftest_bounded_wait",

@@ -1,10 +1,9 @@
 """Forward + backward for callers whose tensors live in HOST memory.
 
-``attention_fwd_bwd_host`` streams the batch through the GPU in chunks on three CUDA streams
-(host->device copies, kernels, device->host copies) with double-buffered device staging, so the
-PCIe transfers in both directions overlap each other and the kernels.  It drives the C ABI
-directly (forward, delta, backward), no autograd graph.  Host tensors should be pinned
-(``tensor.pin_memory()``); pageable memory works but serialises the copies.
+``attention_fwd_bwd_host`` hands host pointers to ``chill_fwd_bwd_host`` of the C ABI (csrc/host_pipeline.cu), which
+streams the batch through the GPU in chunks on three CUDA streams (uploads, kernels, downloads) over two sets of
+device staging buffers, so the PCIe transfers in both directions overlap each other and the kernels.  No autograd
+graph.  Host tensors should be pinned (``tensor.pin_memory()``); pageable memory works but serialises the copies.
 """
 from __future__ import annotations
 
@@ -18,14 +17,26 @@ from .chill import _resolve_functor
 from .mask import ChillMask
 
 
-def _heads_per_chunk(H, G, bytes_per_head, target_bytes):
-    """Largest divisor of H that is a multiple of the GQA group size G and keeps a chunk under target_bytes
-    (at least one group)."""
-    best = G
-    for ch in range(G, H + 1, G):
-        if H % ch == 0 and ch * bytes_per_head <= target_bytes:
-            best = ch
-    return best
+def _host_args(q, k, v, do, out, functor, mask, sm_scale, chunk_groups):
+    a = _cabi.HostArgs()
+    a.s = _cabi.make_shape(q, k, functor, mask.constargs, None, sm_scale,
+                           flags=_cabi.FLAG_BWD_DETERMINISTIC if _cabi.is_deterministic() else 0)
+    a.q, a.k, a.v, a.d_o = (t.data_ptr() for t in (q, k, v, do))
+    a.o, a.dq, a.dk, a.dv = (t.data_ptr() for t in out)
+    a.chunk_groups = chunk_groups
+    return a
+
+
+def chunk_schedule(q, k, mask: ChillMask, chunk_heads: int | None = None):
+    """[(batch row, first kv-head group, groups)] of the chunks a call with these tensors is cut into (host only)."""
+    lib, functor = _resolve_functor(mask)
+    G = q.shape[1] // k.shape[1]
+    a = _host_args(q, k, k, q, (q, q, k, k), functor, mask, 1.0, 0 if chunk_heads is None else max(1, chunk_heads // G))
+    n = lib.chill_host_chunk_schedule(C.byref(a), None, 0)
+    _cabi.check(lib, min(n, 0), "chill_host_chunk_schedule")
+    buf = (C.c_int32 * (3 * n))()
+    lib.chill_host_chunk_schedule(C.byref(a), buf, n)
+    return [tuple(buf[3 * i:3 * i + 3]) for i in range(n)]
 
 
 def attention_fwd_bwd_host(q, k, v, do, mask: ChillMask, sm_scale=None, out=None, chunk_batches: int = 1,
@@ -33,96 +44,42 @@ def attention_fwd_bwd_host(q, k, v, do, mask: ChillMask, sm_scale=None, out=None
     """q, do: [B, H, L, D]; k, v: [B, H_kv, L, D] on the host.  Returns host tensors (o, dq, dk, dv)
     (pinned; pass ``out=(o, dq, dk, dv)`` to reuse buffers).  Synchronises before returning.
 
-    The batch goes through the GPU in chunks of `chunk_batches` batch rows x `chunk_heads` heads (default: up to
-    40 MB of input per chunk, whole GQA groups).  The first chunk's upload and the last chunk's download are the
-    only transfers that nothing overlaps, which favours small chunks, but every chunk costs ~0.3 ms of host time
-    (copies, events, launches): measured on C2 (67 MB per batch row) in one session, 8 chunks of 67 MB reach
-    144 TFLOP/s, 16 chunks of 34 MB 153, 32 chunks of 17 MB 141."""
+    The batch goes through the GPU in chunks of whole GQA groups of one batch row: at most `chunk_heads` heads
+    (default: about CHILL_HOST_CHUNK_MB = 40 MB of input per chunk; measured on C2, 4.2 MB per head: 16 chunks of
+    34 MB reach 155 TFLOP/s, 8 chunks of 67 MB 144).  `chunk_batches` is accepted for compatibility with earlier
+    versions and has no effect."""
     device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     B, H, L, D = q.shape
     Hkv = k.shape[1]
+    assert H % Hkv == 0 and k.shape == v.shape and do.shape == q.shape and q.dtype == k.dtype == v.dtype == do.dtype
+    for t in (q, k, v, do):
+        assert not t.is_cuda, "attention_fwd_bwd_host takes host tensors"
     if sm_scale is None:
         sm_scale = D ** -0.5
     lib, functor = _resolve_functor(mask)
+    q, k, v, do = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v, do))
     if out is None:
         out = tuple(torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, q, k, v))
-    o_h, dq_h, dk_h, dv_h = out
-    cb = max(1, min(chunk_batches, B))
+    for t, like in zip(out, (q, q, k, v)):
+        assert t.shape == like.shape and t.dtype == like.dtype and t.is_contiguous() and not t.is_cuda
     G = H // Hkv
     if chunk_heads is None:
+        per_group = L * D * q.element_size() * (2 * G + 2)
         target = float(os.environ.get("CHILL_HOST_CHUNK_MB", "40")) * 1e6
-        bytes_per_head = cb * L * D * q.element_size() * (2 + 2.0 / G)
-        chunk_heads = _heads_per_chunk(H, G, bytes_per_head, target)
-    ch = max(G, min(H, (chunk_heads // G) * G))
-    if ch < H:
-        cb = 1  # [b, h0:h1] of a contiguous [B, H, L, D] host tensor is one contiguous block only for a single b
-    chk = ch // G
+        big = max(1, min(Hkv, int(target // per_group)))
+        n_chunks = -(-Hkv // big)
+        chunk_groups = -(-Hkv // n_chunks)  # even split of a batch row
+    else:
+        chunk_groups = max(1, min(Hkv, chunk_heads // G))
+    a = _host_args(q, k, v, do, out, functor, mask, float(sm_scale), chunk_groups)
     with torch.cuda.device(device):
-        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-        start = torch.cuda.Event()
-        start.record()  # everything below is ordered after work already queued on the caller's stream
-        for s in (s_in, s_cmp, s_out):
-            s.wait_event(start)
-
-        def dev(shape, dtype):
-            return torch.empty(shape, dtype=dtype, device=device)
-
-        slots = []
-        for _ in range(2):
-            slots.append({
-                "in": [dev((cb, ch, L, D), q.dtype), dev((cb, chk, L, D), q.dtype), dev((cb, chk, L, D), q.dtype),
-                       dev((cb, ch, L, D), q.dtype)],
-                "out": [dev((cb, ch, L, D), q.dtype), dev((cb, ch, L, D), q.dtype), dev((cb, chk, L, D), q.dtype),
-                        dev((cb, chk, L, D), q.dtype)],
-                "lse": dev((cb, ch, L), torch.float32), "delta": dev((cb, ch, L), torch.float32),
-                "in_free": None, "out_free": None,
-            })
-        # fp32 dQ scratch of the single-kernel backward, one per slot like the other staging buffers (allocated
-        # here, on the caller's stream, so that the caching allocator can hand the same blocks out on the next call)
-        shape0 = _cabi.make_shape(slots[0]["in"][0], slots[0]["in"][1], functor, mask.constargs, None, sm_scale)
-        nacc = 0 if _cabi.is_deterministic() else lib.chill_bwd_dq_accum_bytes(C.byref(shape0))
-        for sl in slots:
-            sl["accum"] = dev((nacc // 4,), torch.float32) if nacc else None
-        chunks = [(b0, h0) for b0 in range(0, B, cb) for h0 in range(0, H, ch)]
-        for i, (b0, h0) in enumerate(chunks):
-            b1 = min(B, b0 + cb)
-            n = b1 - b0
-            hs, ks = slice(h0, h0 + ch), slice(h0 // G, h0 // G + chk)
-            sl = slots[i % 2]
-            qd, kd, vd, dod = (t[:n] for t in sl["in"])
-            od, dqd, dkd, dvd = (t[:n] for t in sl["out"])
-            with torch.cuda.stream(s_in):
-                if sl["in_free"] is not None:
-                    s_in.wait_event(sl["in_free"])
-                for dst, src, hsel in zip((qd, kd, vd, dod), (q, k, v, do), (hs, ks, ks, hs)):
-                    dst.copy_(src[b0:b1, hsel], non_blocking=True)
-                ev_in = torch.cuda.Event()
-                ev_in.record(s_in)
-            with torch.cuda.stream(s_cmp):
-                s_cmp.wait_event(ev_in)
-                if sl["out_free"] is not None:
-                    s_cmp.wait_event(sl["out_free"])
-                shape = _cabi.make_shape(qd, kd, functor, mask.constargs, None, sm_scale)
-                _cabi.forward(lib, qd, kd, vd, od, sl["lse"][:n], shape)
-                if sl["accum"] is not None:
-                    _cabi.backward(lib, qd, kd, vd, od, dod, sl["lse"][:n], sl["delta"][:n], dqd, dkd, dvd, shape, sl["accum"])
-                else:
-                    _cabi.backward(lib, qd, kd, vd, od, dod, sl["lse"][:n], sl["delta"][:n], dqd, dkd, dvd, shape,
-                                   deterministic=True)
-                ev_cmp = torch.cuda.Event()
-                ev_cmp.record(s_cmp)
-                sl["in_free"] = ev_cmp
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_cmp)
-                for dst, src, hsel in zip((o_h, dq_h, dk_h, dv_h), (od, dqd, dkd, dvd), (hs, hs, ks, ks)):
-                    dst[b0:b1, hsel].copy_(src, non_blocking=True)
-                ev_out = torch.cuda.Event()
-                ev_out.record(s_out)
-                sl["out_free"] = ev_out
-        cur = torch.cuda.current_stream()
-        for s in (s_in, s_cmp, s_out):
-            ev = torch.cuda.Event()
-            ev.record(s)
-            cur.wait_event(ev)
-        cur.synchronize()
-    return o_h, dq_h, dk_h, dv_h
+        nbytes = lib.chill_host_workspace_bytes(C.byref(a))
+        if nbytes == 0:
+            raise ValueError("chill_fwd_bwd_host: unsupported arguments")
+        work = torch.empty(nbytes + 256, dtype=torch.uint8, device=device)
+        base = (work.data_ptr() + 255) // 256 * 256
+        a.workspace, a.workspace_bytes = base, nbytes
+        stream = torch.cuda.current_stream()
+        _cabi.check(lib, lib.chill_fwd_bwd_host(C.byref(a), C.c_void_p(stream.cuda_stream)), "chill_fwd_bwd_host")
+        stream.synchronize()  # outputs are in host memory; `work` may go back to the allocator
+    return out

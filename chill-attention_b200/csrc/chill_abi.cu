@@ -25,6 +25,8 @@ static int cuda_fail(cudaError_t e, const char* what) {
   return CHILL_E_CUDA;
 }
 
+int record_cuda_failure(cudaError_t e, const char* what) { return cuda_fail(e, what); }  // for host_pipeline.cu
+
 static int* device_status_ptr() {
   // one word per device (the symbol is instantiated in every device's module image)
   int* p = nullptr;

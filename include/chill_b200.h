@@ -13,6 +13,9 @@
  *    device from different streams;
  *  - for chill_bwd_noalloc, a 16 MiB array in device global memory per GPU (part of
  *    the library image) and a per-device cache of its address;
+ *  - for chill_fwd_bwd_host, three streams and a handful of events per device (created on the
+ *    first call) that carry its upload / compute / download pipeline; a per-device lock
+ *    serialises the host side of concurrent calls;
  *  - a process-wide count of launched kernels (chill_launch_count).
  * All work is enqueued on the CUDA stream passed in (a cudaStream_t cast to
  * void*; NULL = the default stream) of the CURRENT device.  Return value: 0 on
@@ -45,7 +48,7 @@
 extern "C" {
 #endif
 
-#define CHILL_ABI_VERSION 4
+#define CHILL_ABI_VERSION 5
 
 /* status codes */
 #define CHILL_OK 0
@@ -197,6 +200,39 @@ int chill_bwd(const chill_bwd_args* a, void* stream);
  *    dependency between them - race on it.  Serialise them (same stream, or an event). */
 #define CHILL_NOALLOC_MAX_ROWS (1u << 22)
 int chill_bwd_noalloc(const chill_bwd_args* a, void* stream);
+
+/* Forward + backward for a caller whose tensors live in HOST memory (no counterpart in the reference, whose
+ * tensors are torch CUDA tensors; this is the call an embedder with host-resident activations makes, and what
+ * the end-to-end figure of the benchmark times).
+ *
+ * q, d_o, o, dq: contiguous [B][H][L][D]; k, v, dk, dv: contiguous [B][H_kv][L][D]; L = s.Lq = s.Lk = s.seq_len,
+ * offsets 0, s.lens NULL (CHILL_E_INVALID otherwise).  Host memory should be page-locked: pageable memory works
+ * but its copies do not overlap anything.
+ *
+ * The batch goes through the GPU in chunks of `chunk_groups` whole kv-head groups of one batch row, on three
+ * streams (uploads, kernels, downloads) over two sets of device staging buffers carved from `workspace`, so
+ * transfers in both directions overlap each other and the kernels.  Per chunk it calls chill_fwd, chill_bwd_delta
+ * and chill_bwd (single-kernel backward with the fp32 dQ scratch unless CHILL_FLAG_BWD_DETERMINISTIC is set in
+ * s.flags).
+ *
+ * The work is ordered after everything already enqueued on `stream`, and `stream` is made to wait for all of it;
+ * the call itself does not synchronise: synchronise `stream` before reading the outputs or reusing `workspace`. */
+#define CHILL_FLAG_BWD_DETERMINISTIC 32u /* chill_fwd_bwd_host: two-kernel backward (no fp32 dQ scratch) */
+typedef struct chill_host_args {
+  chill_shape s;
+  const void *q, *k, *v, *d_o; /* host */
+  void *o, *dq, *dk, *dv;      /* host */
+  void* workspace;             /* device, 256-byte aligned, chill_host_workspace_bytes() bytes */
+  size_t workspace_bytes;
+  int32_t chunk_groups;        /* kv-head groups per full-size chunk; 0 = about 40 MB of input per chunk */
+  int32_t reserved;
+} chill_host_args;
+size_t chill_host_workspace_bytes(const chill_host_args* a);
+int chill_fwd_bwd_host(const chill_host_args* a, void* stream);
+/* The chunk schedule chill_fwd_bwd_host would run for these arguments (host-only, pointers in `a` are not
+ * looked at): up to `capacity` triples (batch row, first kv-head group, groups) are written to `out` (may be
+ * NULL); returns the number of chunks or a negative status. */
+int chill_host_chunk_schedule(const chill_host_args* a, int32_t* out, int32_t capacity);
 
 /* Bytes of the `delta` scratch buffer chill_bwd_delta / chill_bwd need. */
 size_t chill_bwd_scratch_bytes(const chill_shape* s);

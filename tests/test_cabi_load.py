@@ -1,5 +1,7 @@
 """The C-ABI library builds, loads without a GPU and exports what include/chill_b200.h declares."""
 import ctypes
+
+import torch
 import os
 import re
 
@@ -44,7 +46,7 @@ def test_struct_sizes_match_header(lib):
 
 
 def test_host_only_entry_points(lib):
-    assert lib.chill_abi_version() == 4
+    assert lib.chill_abi_version() == 5
     assert lib.chill_status_string(0) == b"ok"
     assert b"invalid" in lib.chill_status_string(-1)
     # bit0 k full range, bit1 q full range, bit2/3 continuous limits, bit4 guaranteed safe
@@ -94,3 +96,23 @@ def test_no_cuda_means_error_not_fallback(lib):
     q = torch.randn(1, 1, 8, 16)
     with pytest.raises(Exception):
         chill_attention(q, q, q, mask=CausalChillMask())
+
+
+def test_host_pipeline_chunk_schedule():
+    """Every (batch row, kv-head group) exactly once, in order, no chunk above the limit."""
+    import chill_attention as ca
+    from chill_attention.host import chunk_schedule
+
+    mask = ca.CausalChillMask()
+    for B, H, Hkv, heads in [(8, 16, 16, 8), (1, 32, 32, 4), (2, 8, 4, 4), (1, 2, 2, 1), (3, 10, 5, 4), (1, 1, 1, 1),
+                             (4, 7, 7, 16), (8, 16, 16, None)]:
+        q = torch.empty(B, H, 4096, 128, dtype=torch.bfloat16, device="meta")
+        k = torch.empty(B, Hkv, 4096, 128, dtype=torch.bfloat16, device="meta")
+        sch = chunk_schedule(q, k, mask, heads)
+        big = Hkv if heads is None else max(1, min(Hkv, heads // (H // Hkv)))
+        covered = sorted((b, g) for b, g0, n in sch for g in range(g0, g0 + n))
+        assert covered == [(b, g) for b in range(B) for g in range(Hkv)]
+        assert all(1 <= n <= big for _, _, n in sch)
+        assert [b for b, _, _ in sch] == sorted(b for b, _, _ in sch)
+    # default: about 40 MB of input per chunk -> C2 (4.2 MB per head) gets 8 heads per full-size chunk
+    assert max(n for _, _, n in sch) == 8

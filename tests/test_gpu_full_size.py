@@ -62,7 +62,11 @@ def test_sampled_rows_and_identities(name):
     gen = torch.Generator().manual_seed(1)
     # ---- forward + dQ on sampled query rows (including first/last rows and tile edges)
     rows = torch.cat([torch.tensor([0, 1, 127, 128, 129, L - 129, L - 128, L - 1]), torch.randint(0, L, (56,), generator=gen)]).unique()
-    for bi, hi in ((0, 0), (B - 1, H - 1)):
+    # the corner (batch, head) units plus two drawn at random: a wrong tile in any head must be able to show
+    units = {(0, 0), (B - 1, H - 1)}
+    while len(units) < 4:
+        units.add((int(torch.randint(0, B, (1,), generator=gen)), int(torch.randint(0, H, (1,), generator=gen))))
+    for bi, hi in sorted(units):
         for r in rows.tolist():
             lo, hi_k = (int(x) for x in cls.k_range_for_q(r, L, margs))
             kp = torch.arange(lo, hi_k + 1)
@@ -80,25 +84,26 @@ def test_sampled_rows_and_identities(name):
             assert err <= 2 * G_RTOL[dtype] * dq_ref.norm().item() + 2e-2, (name, "dq", r, err)
     # ---- dK / dV on sampled key rows
     keys = torch.cat([torch.tensor([0, 127, 128, L - 1]), torch.randint(0, L, (12,), generator=gen)]).unique()
-    bi, hi = B - 1, 0
-    for kk in keys.tolist():
-        lo, hi_q = (int(x) for x in cls.q_range_for_k(kk, L, margs))
-        qp = torch.arange(lo, hi_q + 1)
-        # P needs the full softmax row of every query that sees this key: use the stored LSE instead
-        qs = q[bi, hi, lo:hi_q + 1].detach().cpu().double()
-        dos = do[bi, hi, lo:hi_q + 1].cpu().double()
-        os_ = o[bi, hi, lo:hi_q + 1].detach().cpu().double()
-        lses = lse[bi, hi, lo:hi_q + 1].cpu().double()
-        kv, vv = k[bi, hi, kk].detach().cpu().double(), v[bi, hi, kk].detach().cpu().double()
-        vis = orc.builtin_mask_dense(mname, margs, qp, torch.tensor([kk]))[:, 0]
-        s2 = (qs @ kv) * (D ** -0.5) * orc.LOG2E
-        p = torch.where(vis, torch.exp2(s2 - lses), torch.zeros_like(s2))
-        dv_ref = p @ dos
-        ds = p * (dos @ vv - (os_ * dos).sum(-1))
-        dk_ref = (ds @ qs) * (D ** -0.5)
-        for nm, mine, ref in (("dv", v.grad[bi, hi, kk], dv_ref), ("dk", k.grad[bi, hi, kk], dk_ref)):
-            err = (mine.cpu().double() - ref).norm().item()
-            assert err <= 3 * G_RTOL[dtype] * ref.norm().item() + 2e-2, (name, nm, kk, err)
+    key_units = [(B - 1, 0), (int(torch.randint(0, B, (1,), generator=gen)), int(torch.randint(0, H, (1,), generator=gen)))]
+    for bi, hi in key_units:
+        for kk in keys.tolist():
+            lo, hi_q = (int(x) for x in cls.q_range_for_k(kk, L, margs))
+            qp = torch.arange(lo, hi_q + 1)
+            # P needs the full softmax row of every query that sees this key: use the stored LSE instead
+            qs = q[bi, hi, lo:hi_q + 1].detach().cpu().double()
+            dos = do[bi, hi, lo:hi_q + 1].cpu().double()
+            os_ = o[bi, hi, lo:hi_q + 1].detach().cpu().double()
+            lses = lse[bi, hi, lo:hi_q + 1].cpu().double()
+            kv, vv = k[bi, hi, kk].detach().cpu().double(), v[bi, hi, kk].detach().cpu().double()
+            vis = orc.builtin_mask_dense(mname, margs, qp, torch.tensor([kk]))[:, 0]
+            s2 = (qs @ kv) * (D ** -0.5) * orc.LOG2E
+            p = torch.where(vis, torch.exp2(s2 - lses), torch.zeros_like(s2))
+            dv_ref = p @ dos
+            ds = p * (dos @ vv - (os_ * dos).sum(-1))
+            dk_ref = (ds @ qs) * (D ** -0.5)
+            for nm, mine, ref in (("dv", v.grad[bi, hi, kk], dv_ref), ("dk", k.grad[bi, hi, kk], dk_ref)):
+                err = (mine.cpu().double() - ref).norm().item()
+                assert err <= 3 * G_RTOL[dtype] * ref.norm().item() + 2e-2, (name, nm, kk, err)
     # ---- checksum identity: sum over keys of dV equals sum over queries of dO
     lhs = v.grad.double().sum(dim=2)
     rhs = do.double().sum(dim=2)

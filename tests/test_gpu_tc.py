@@ -198,6 +198,20 @@ def test_host_buffer_pipeline_matches_device_path():
     assert torch.equal(dkh, grads[1].cpu()) and torch.equal(dvh, grads[2].cpu())
     rel = ((dqh.double() - grads[0].cpu().double()).norm() / grads[0].cpu().double().norm()).item()
     assert rel <= 1e-2
+    # many head groups per batch row, a chunk size that does not divide them: still bit for bit
+    mask = ca.SlidingWindowChillMask(100, 0)
+    for B in (1, 3):
+        q, k, v, do = make_inputs(B, 16, 8, 256, 64, torch.float16, seed=5)
+        host = [t.pin_memory() for t in (q, k, v, do)]
+        ca.set_deterministic(True)
+        try:
+            o, lse, grads = run(mask, q, k, v, do)
+            oh, dqh, dkh, dvh = attention_fwd_bwd_host(*host, mask, chunk_heads=6)
+            assert torch.equal(oh, o.detach().cpu())
+            for a, b in zip((dqh, dkh, dvh), grads):
+                assert torch.equal(a, b.cpu())
+        finally:
+            ca.set_deterministic(False)
 
 
 @pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64), (torch.float32, 32)], ids=str)
