@@ -301,11 +301,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t sQ = base + L::kQ, sK = base + L::kK, sV = base + L::kV;
   const uint32_t bars = base + L::kBars;
   constexpr int NSB = SH::kSBufs;
-  // s_full / p_full: one barrier per S buffer (bars + 8, + 16 / bars + 24, + 32); pv_done counts finished O += P V
-  const uint32_t bar_q_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 24, bar_o_full = bars + 40,
-                 bar_pv_done = bars + 48;
-  const uint32_t bar_k_full = bars + 64, bar_k_empty = bar_k_full + 8 * NSTAGE, bar_v_full = bar_k_empty + 8 * NSTAGE,
-                 bar_v_empty = bar_v_full + 8 * NSTAGE;
+  // One tcgen05.commit per MMA batch is free, a second one costs the issuing thread ~48 clocks (measured), so a
+  // batch signals ONE barrier with several waiters: s_full[j % NSTAGE] tells the softmax warps that S(j) is there
+  // and the producer that K stage j % NSTAGE is free; v_empty[j % NSTAGE] tells the producer that V stage is free
+  // and a softmax warp that has to rescale O that O += P(j) V(j) has finished.  Per barrier at most one phase can
+  // be ahead of any waiter (the next commit on it needs that waiter's own progress), so the parity tests hold.
+  // p_full: one barrier per S buffer.
+  const uint32_t bar_q_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 24, bar_o_full = bars + 40;
+  const uint32_t bar_k_full = bars + 64, bar_v_full = bar_k_full + 8 * NSTAGE, bar_v_empty = bar_v_full + 8 * NSTAGE;
+  const uint32_t bar_k_empty = bar_s_full;  // same barriers: S(j) complete == K stage j % NSTAGE consumed
+  static_assert(NSTAGE <= 2 && NSB <= 2, "barrier layout");
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
   const Guard guard{p.status, abort_flag};
@@ -316,15 +321,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (lane == 0) {
       *abort_flag = 0;
       mbar_init(bar_q_full, 1);
-      for (int i = 0; i < NSB; ++i) {
-        mbar_init(bar_s_full + 8 * i, 1);
-        mbar_init(bar_p_full + 8 * i, 4);
-      }
+      for (int i = 0; i < NSB; ++i) mbar_init(bar_p_full + 8 * i, 4);
       mbar_init(bar_o_full, 1);
-      mbar_init(bar_pv_done, 1);
       for (int s = 0; s < NSTAGE; ++s) {
+        mbar_init(bar_s_full + 8 * s, 1);
         mbar_init(bar_k_full + 8 * s, 1);
-        mbar_init(bar_k_empty + 8 * s, 1);
         mbar_init(bar_v_full + 8 * s, 1);
         mbar_init(bar_v_empty + 8 * s, 1);
       }
@@ -395,8 +396,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int kk = 0; kk < D / 16; ++kk)  // Q chunks are 128 rows apart, K chunks KT rows
           mma_ss_lh(ts, q_lo + kmajor_step(kk), k_lo + (uint32_t)((kk / 4) * (kKvChunkBytes / 16) + (kk % 4) * 2), hi_k, idesc_s,
                     kk > 0 ? 1u : 0u);
-        mma_commit(bar_k_empty + 8 * s);
-        mma_commit(bar_s_full + 8 * (j % NSB));
+        mma_commit(bar_s_full + 8 * s);
         return true;
       };
       auto issue_pv = [&](int j) -> bool {  // O += P(j) V(j): P (16-bit) from TMEM, 16 keys = 8 columns per MMA
@@ -410,7 +410,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int kk = 0; kk < KT / 16; ++kk)
           mma_ts_lh(tO, tp + kk * 8, v_lo + kk * 128, hi_k, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         mma_commit(bar_v_empty + 8 * s);
-        if (NSB > 1) mma_commit(bar_pv_done);
         return true;
       };
       if (NSB == 1) {
@@ -444,7 +443,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int j = 0; j < n_tiles; ++j) {
       const int kt = kt_lo + j;
       const int kg0 = kt * KT + g.k_off;
-      ok = mbar_wait(bar_s_full + 8 * (j % NSB), (uint32_t)(j / NSB) & 1u, guard, kStSoftmax);
+      ok = mbar_wait(bar_s_full + 8 * (j % NSTAGE), (uint32_t)(j / NSTAGE) & 1u, guard, kStSoftmax);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
@@ -452,7 +451,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                         kt * KT + KT <= g.Lk;
       const int klim = imin(n - kg0, g.Lk - kt * KT);  // columns >= klim do not exist
       softmax_tile<T, D, M, KT>(tS + (uint32_t)((j % NSB) * KT), tO, lane_sel, j == 0, full, klim, qg, kg0, n, g.margs, c,
-                                m_used, l, NSB > 1 ? bar_pv_done : 0u, (uint32_t)(j - 1) & 1u, &guard);
+                                m_used, l, NSB > 1 ? bar_v_empty + 8 * (uint32_t)((j - 1) % NSTAGE) : 0u,
+                                (uint32_t)((j - 1) / NSTAGE) & 1u, &guard);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
