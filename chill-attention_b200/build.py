@@ -25,6 +25,9 @@ BUILTIN_FUNCTORS = ("FullMask", "CausalMask", "SlidingWindowMask", "ChunkwiseMas
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-I" + INCLUDE, "-I" + CSRC,
+    # several builds of these sources can live in one process (the main library and custom-mask libraries): keep
+    # their function-local statics apart instead of merging them as process-wide unique symbols
+    "-Xcompiler", "-fno-gnu-unique",
 ]
 
 

@@ -324,7 +324,7 @@ bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     }
-    if (lane == 0) tma_store_wait_all();  // shared memory is read and the sums are in global memory before the CTA ends
+    if (lane == 0) bulk_wait_read<0>();  // the staging buffers have been read; the sums land in global memory by kernel end
   } else {
     // ------------------------------------------------------------------- compute warps
     reg_alloc<kFusedComputeRegs>();

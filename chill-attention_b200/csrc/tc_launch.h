@@ -18,8 +18,11 @@ struct BwdTcParams;
 // Raises a kernel's dynamic shared-memory limit the first time the kernel is launched on a device.  The attribute
 // is per (kernel, device); the record of where it has been set is per call site (pass a distinct `Tag` per kernel)
 // and guarded by a mutex, so host threads driving different devices do not race on it.
+// `static`: the record must stay private to one copy of the library.  As an inline function its local statics become
+// process-wide unique symbols, and a second library built from the same sources (a custom-mask build) loaded into
+// the same process would find "already set" for kernels of its own that never had their limit raised.
 template <class Tag, class Kern>
-inline cudaError_t ensure_dynamic_smem(Kern kern, int smem_bytes, bool prefer_max_carveout = false) {
+static cudaError_t ensure_dynamic_smem(Kern kern, int smem_bytes, bool prefer_max_carveout = false) {
   constexpr int kMaxDevices = 64;
   static bool done[kMaxDevices] = {};
   static std::mutex mu;

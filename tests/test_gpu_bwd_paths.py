@@ -317,3 +317,35 @@ def test_two_host_threads_run_the_two_kernel_backward_on_one_device(lib):
     for want, got in zip(serial, results):
         for x, y in zip(want, got):
             assert torch.equal(x, y)
+
+
+def test_two_copies_of_the_library_in_one_process(tmp_path):
+    """A custom-mask build is a second library made from the same sources.  Each copy keeps its own record of which
+    kernels had their shared-memory limit raised: if the copies shared it, the second one would launch kernels whose
+    limit was never set ("invalid argument")."""
+    import shutil
+
+    import chill_attention as ca
+    from chill_attention import _cabi
+
+    second = str(tmp_path / "libchill_b200_copy.so")
+    shutil.copy(_cabi.DEFAULT_LIB, second)
+    libs = [_cabi.load_library(), _cabi.load_library(second)]
+    assert libs[0] is not libs[1]
+    mask = ca.CausalChillMask()
+    q, k, v, do = (t.cuda() for t in make_inputs(1, 2, 2, 300, 128, torch.bfloat16))
+    shape = _cabi.make_shape(q, k, _cabi.BUILTIN_FUNCTOR_IDS[mask.cuda_functor], mask.constargs, None, 128 ** -0.5)
+    outs = []
+    for lib in libs:
+        o = torch.empty_like(q)
+        lse = torch.empty(q.shape[:3], dtype=torch.float32, device="cuda")
+        _cabi.forward(lib, q, k, v, o, lse, shape)
+        delta = torch.empty_like(lse)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        for deterministic in (False, True):  # single-kernel and two-kernel backward: different kernels, each set up once
+            _cabi.backward(lib, q, k, v, o, do, lse, delta, dq, dk, dv, shape, deterministic=deterministic)
+        torch.cuda.synchronize()
+        assert lib.chill_read_device_status() == 0
+        outs.append((o, dq, dk, dv))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
