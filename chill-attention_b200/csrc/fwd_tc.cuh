@@ -176,13 +176,16 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   const float m_safe = (m_used == -CUDART_INF_F) ? 0.f : m_used;
   const uint64_t c2 = pk2(c, c), nm2 = pk2(-m_safe, -m_safe);
   uint64_t l0 = 0ull, l1 = 0ull;  // two packed partial row sums (+0.0f, +0.0f)
+  // Share of the pairs whose 2^x is the polynomial on the FMA pipe instead of MUFU.  Head dim 256 runs one CTA per
+  // SM, i.e. one softmax warp per scheduler with nothing to hide its MUFU latency behind: a quarter there measured
+  // 1.155 vs 1.211 ms (causal L = 4096); every share made head dims 64 / 128 slower (see tc_common.cuh).
+  constexpr int kPolyNum = (D == 256 && CHILL_FWD_POLY_NUM == 0) ? 1 : CHILL_FWD_POLY_NUM;
+  constexpr int kPolyDen = (D == 256 && CHILL_FWD_POLY_NUM == 0) ? 4 : CHILL_FWD_POLY_DEN;
 #pragma unroll
   for (int i = 0; i < KT / 2; i += 2) {
-    // two pairs per step; a fixed share of the pairs takes the polynomial 2^x (FMA pipe), the rest MUFU
-    const uint64_t e0 = ex2_pair(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nm2),
-                                 (i % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
-    const uint64_t e1 = ex2_pair(ffma2(pk2u(sreg[2 * i + 2], sreg[2 * i + 3]), c2, nm2),
-                                 ((i + 1) % CHILL_FWD_POLY_DEN) < CHILL_FWD_POLY_NUM);
+    // two pairs per step
+    const uint64_t e0 = ex2_pair(ffma2(pk2u(sreg[2 * i], sreg[2 * i + 1]), c2, nm2), (i % kPolyDen) < kPolyNum);
+    const uint64_t e1 = ex2_pair(ffma2(pk2u(sreg[2 * i + 2], sreg[2 * i + 3]), c2, nm2), ((i + 1) % kPolyDen) < kPolyNum);
     l0 = fadd2(l0, e0);
     l1 = fadd2(l1, e1);
     float p0, p1, p2, p3;

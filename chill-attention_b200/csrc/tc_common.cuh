@@ -348,7 +348,9 @@ __device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
 // Default 0: measured on B200 (causal and full masks, L = 4096, D = 128) every non-zero share made the
 // forward slower (0.60 ms at 0 %, 0.62 at 25 %, 0.65 at 50 %, 0.67 at 75 %) and the backward no faster:
 // the kernels are bound by the dependency chain between MMA and softmax phases, not by MUFU throughput.
-// The path is kept (and covered by the parity tests when enabled) for shapes where that changes.
+// The same holds for head dim 64 (chunkwise L = 16384: 0.372 ms at 0 %, 0.380 at 25 %, 0.418 at 50 %).  The one
+// shape where it pays is the forward for head dim 256 (one CTA per SM): a quarter is switched on there in
+// fwd_tc.cuh whatever these macros say, and covered by that kernel's parity tests.
 #ifndef CHILL_FWD_POLY_NUM
 #define CHILL_FWD_POLY_NUM 0
 #endif
