@@ -903,9 +903,41 @@ def run_reference_shapes(args):
                     e1.record()
                     torch.cuda.synchronize()
                     res[what] = e0.elapsed_time(e1) / args.steps
+                    # the same call replayed from a CUDA graph (no host time per call), which is how the reference's
+                    # script measures (benchmark/benchmark.py:263-264, triton.testing.do_bench_cudagraph)
+                    res[what + "_graph"] = None
+                    for attempt in range(0 if args.no_cuda_graph else 2):  # a process's first capture of a path can
+                        try:                                                # meet one-time set-up: one more try
+                            side = torch.cuda.Stream()
+                            side.wait_stream(torch.cuda.current_stream())
+                            with torch.cuda.stream(side):
+                                fn()
+                            torch.cuda.current_stream().wait_stream(side)
+                            graph = torch.cuda.CUDAGraph()
+                            n_in_graph = 10
+                            with torch.cuda.graph(graph):
+                                for _ in range(n_in_graph):
+                                    fn()
+                            graph.replay()
+                            torch.cuda.synchronize()
+                            e0.record()
+                            for _ in range(max(1, args.steps // 2)):
+                                graph.replay()
+                            e1.record()
+                            torch.cuda.synchronize()
+                            res[what + "_graph"] = e0.elapsed_time(e1) / (max(1, args.steps // 2) * n_in_graph)
+                            res.pop(what + "_graph_error", None)
+                            del graph
+                            break
+                        except Exception as exc:  # noqa: BLE001 - reported in the line, the eager figures stand
+                            res[what + "_graph_error"] = repr(exc)[:200]
+                            torch.cuda.synchronize()
                 pairs = unmasked_pairs(mask, T)
                 print(json.dumps({"mask": str(mask), "shape": name, "batch": 8, "heads": heads, "dim": dim, "time": T,
                                   "dtype": "f16", "fwd_ms": round(res["fwd"], 4), "bwd_ms": round(res["bwd"], 4),
+                                  "fwd_graph_ms": None if res["fwd_graph"] is None else round(res["fwd_graph"], 4),
+                                  "bwd_graph_ms": None if res["bwd_graph"] is None else round(res["bwd_graph"], 4),
+                                  **{k_: v_ for k_, v_ in res.items() if k_.endswith("_error")},
                                   "fwd_tflops": round(4.0 * 8 * heads * dim * pairs / res["fwd"] / 1e9, 1),
                                   "bwd_tflops": round(10.0 * 8 * heads * dim * pairs / res["bwd"] / 1e9, 1)}), flush=True)
 
@@ -921,6 +953,7 @@ def main():
     ap.add_argument("--bwd", default="fused", choices=("fused", "split"), help="form of the backward pass")
     ap.add_argument("--reference-shapes", action="store_true",
                     help="time the shapes of the reference's own benchmark script instead of a workload")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="--reference-shapes: skip the CUDA-graph replay timings")
     ap.add_argument("--blocks", type=int, default=5, help="the K-step block is timed this many times; the median is reported")
     ap.add_argument("--block-gap-ms", type=float, default=300.0,
                     help="idle time before each timed repetition, so that each starts from the same power state")

@@ -415,3 +415,39 @@ def test_eager_call_path_equals_the_dispatcher_ops(_lib):
     with torch.no_grad():
         o = ca.chill_attention(q.cuda(), k.cuda(), v.cuda(), mask=mask)
     assert isinstance(o, torch.Tensor) and not o.requires_grad
+
+
+def test_forward_and_backward_replay_from_a_cuda_graph():
+    """chill_attention() and its backward enqueue on the current stream without synchronising or allocating outside
+    torch's allocator, so a caller can capture them in a CUDA graph (how the reference's benchmark script times its
+    kernels, benchmark/benchmark.py:263-264).  Replays with new input values must give what eager calls give."""
+    import chill_attention as ca
+
+    mask = ca.SlidingWindowChillMask(16, 16)
+    q, k, v, do = (t.cuda() for t in make_inputs(2, 4, 2, 520, 128, torch.float16, seed=51))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+
+    def step():
+        o = ca.chill_attention(q, k, v, mask=mask)
+        gq, gk, gv = torch.autograd.grad(o, (q, k, v), do)
+        return o, gq, gk, gv
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()  # one-time set-up of the kernels happens outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = step()
+    with torch.no_grad():  # new values in the captured input buffers
+        for t, s_ in zip((q, k, v, do), make_inputs(2, 4, 2, 520, 128, torch.float16, seed=52)):
+            t.copy_(s_.cuda())
+    graph.replay()
+    torch.cuda.synchronize()
+    eager = step()
+    assert torch.equal(outs[0], eager[0])
+    assert torch.equal(outs[2], eager[2]) and torch.equal(outs[3], eager[3])  # dK, dV are deterministic
+    rel = ((outs[1].double() - eager[1].double()).norm() / eager[1].double().norm()).item()
+    assert rel <= 1e-2  # dQ: fp32 reductions in an order that is not fixed
