@@ -75,7 +75,7 @@ def test_lens_and_gqa(lib, mask, heads):
     H, Hkv = heads
     L, dtype = 520, torch.bfloat16
     q, k, v, do = make_inputs(4, H, Hkv, L, 128, dtype, seed=32)
-    lens = torch.tensor([L, 1, 130, L + 1], dtype=torch.int32)
+    lens = torch.tensor([L, 0, 130, L + 1], dtype=torch.int32)
     fused, split = _run_both(lib, mask, q, k, v, do, lens)
     _check_pair(fused, split, dtype)
     g_ref = oracle_all(mask, q, k, v, do, lens)[2:]

@@ -291,7 +291,7 @@ def test_fp32_forward_in_tf32_with_lens_and_ragged_length(_lib):
     from chill_attention import chill_attention
 
     L, D = 333, 64
-    lens = torch.tensor([L, 1, 130, 200], dtype=torch.int32)
+    lens = torch.tensor([L, 0, 130, 200], dtype=torch.int32)
     for mask in (ca.CausalChillMask(), ca.SlidingWindowChillMask(50, 7)):
         q, k, v, do = make_inputs(4, 6, 2, L, D, torch.float32, seed=52)
         o_ref, lse_ref, *_ = oracle_all(mask, q, k, v, do, lens)
