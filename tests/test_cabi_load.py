@@ -116,3 +116,30 @@ def test_host_pipeline_chunk_schedule():
         assert [b for b, _, _ in sch] == sorted(b for b, _, _ in sch)
     # default: about 40 MB of input per chunk -> C2 (4.2 MB per head) gets 8 heads per full-size chunk
     assert max(n for _, _, n in sch) == 8
+
+
+def test_header_is_plain_c(tmp_path):
+    """include/chill_b200.h is what a C / cgo / JNI host includes: it must compile as C99 without CUDA headers, and a
+    C program that takes the address of every declared entry point must link against the library."""
+    import shutil
+    import subprocess
+
+    from chill_attention import _cabi
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    inc = os.path.join(ROOT, "include")
+    src = tmp_path / "use_abi.c"
+    calls = "\n".join(f"  p[{i}] = (void*)&{name};" for i, name in enumerate(_cabi.EXPORTS))
+    src.write_text('#include "chill_b200.h"\n#include <stdio.h>\nint main(void) {\n'
+                   f"  void* p[{len(_cabi.EXPORTS)}];\n{calls}\n"
+                   '  chill_host_args a = {0};\n  chill_bwd_args b = {0};\n  (void)a; (void)b;\n'
+                   '  printf("%d %d\\n", chill_abi_version(), p[0] != 0);\n  return 0;\n}\n')
+    exe = tmp_path / "use_abi"
+    lib_dir = os.path.dirname(_cabi.DEFAULT_LIB)
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", inc, str(src), "-o", str(exe), "-L", lib_dir,
+                        "-l:libchill_b200.so", f"-Wl,-rpath,{lib_dir}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.split() == [str(_cabi.ABI_VERSION), "1"], out.stdout + out.stderr
