@@ -73,3 +73,39 @@ def test_sequence_sharded_on_two_gpus(mask, use_buffers):
     ensure_built()
     port = 29600 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(2, port, mask[0], mask[1], 2048, "bfloat16", use_buffers), nprocs=2, join=True)
+
+
+def test_tensors_on_a_device_that_is_not_current():
+    """One process, two GPUs: calls for tensors on cuda:1 while cuda:0 is the current device (and the other way
+    round afterwards).  The library keeps its per-kernel set-up, status word and helper streams per device."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ensure_built()
+    import chill_attention as ca
+    from chill_attention import _cabi
+    from helpers import check_forward, check_grads, make_inputs, oracle_all
+
+    lib = _cabi.load_library()
+    mask = ca.SlidingWindowChillMask(200, 0)
+    for dtype, D in ((torch.bfloat16, 128), (torch.float32, 32)):
+        q, k, v, do = make_inputs(2, 4, 2, 520, D, dtype, seed=61)
+        o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+        for current, other in ((0, 1), (1, 0)):
+            torch.cuda.set_device(current)
+            dev = torch.device("cuda", other)
+            qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+            for deterministic in (False, True):
+                ca.set_deterministic(deterministic)
+                try:
+                    o, lse = ca.chill_attention(qd, kd, vd, mask=mask, return_lse=True)
+                    grads = torch.autograd.grad(o, (qd, kd, vd), do.to(dev))
+                finally:
+                    ca.set_deterministic(False)
+                assert o.device == dev and all(g.device == dev for g in grads)
+                check_forward(o, lse, o_ref, lse_ref, None, dtype)
+                check_grads(grads, g_ref, dtype)
+            for d in (0, 1):
+                with torch.cuda.device(d):
+                    torch.cuda.synchronize()
+                    assert lib.chill_read_device_status() == 0
+    torch.cuda.set_device(0)
