@@ -53,20 +53,22 @@ __device__ __forceinline__ void cta_order(int idx, int n_hb, int n_tiles, int& h
   hb = grp * group + (rem - rank * heads_here);
 }
 constexpr int kFwdThreads = 256;      // warps 0-3 softmax, 4 TMA producer, 5 MMA issuer, 6-7 idle
-constexpr int kFwdSoftmaxRegs = 200;  // per-thread register budget after setmaxnreg (2 CTAs/SM:
-constexpr int kFwdOtherRegs = 56;     //   2 * 128 * (200 + 56) = 65536)
-constexpr int kTmemColsFwd = 256;
+constexpr int kFwdSoftmaxRegs = 200;  // TF32 forward (fwd_tf32.cuh): per-thread register budget after setmaxnreg
+constexpr int kFwdOtherRegs = 56;     //   (2 CTAs/SM: 2 * 128 * (200 + 56) = 65536)
+constexpr int kTmemColsFwd = 256;     // TF32 forward: S 128 + O 128 columns
 
-// Shape of the 16-bit forward kernel for one head dimension.  The kernel is bound by the latency of its per-tile
-// chain S = Q K^T -> softmax -> O += P V (the next S overwrites P, so the steps of one CTA cannot overlap; measured
-// ~4100 clocks per 128-key tile per CTA against 1024 clocks of tensor work), so what counts is how many such chains an
-// SM runs side by side, which TMEM (512 columns: S + O per CTA) limits.  D = 128: S 128 + O 128 columns, two CTAs.
-// D = 64: key tiles of 64 keys need S 64 + O 64 = 128 columns, four CTAs; the narrower MMAs (N = 64) run at 2/3 of
-// the rate, which the kernel does not feel.  D = 128 spends its 256 columns on O and TWO 64-key S buffers instead:
-// S(j+1) = Q K(j+1)^T is issued before O += P(j) V(j), so it runs while the softmax warps work on tile j and the
-// chain of a CTA shrinks to softmax -> PV.  A CTA's register pool is threads x launch registers, and the softmax
-// warpgroup's setmaxnreg.inc is only ever granted if softmax + other <= 2 x launch.
+// Shape of the 16-bit forward kernel for one head dimension.  With one S buffer per CTA the steps of a tile form
+// a chain S = Q K^T -> softmax -> O += P V -> next S (the next S overwrites P), measured at ~4100 clocks per 128-key
+// tile against 1024 clocks of tensor work; what counts then is how many such chains an SM runs side by side, which
+// TMEM (512 columns: S + O per CTA) limits.
+// D = 64: key tiles of 64 keys need S 64 + O 64 = 128 columns, four CTAs per SM; the narrower MMAs (N = 64) run at
+// 2/3 of the rate, which the kernel does not feel.
+// D = 128: two CTAs per SM, 256 columns each, spent on O and TWO 64-key S buffers: S(j+1) = Q K(j+1)^T is issued
+// before O += P(j) V(j), so it runs while the softmax warps work on tile j and the chain of a CTA shrinks to
+// softmax -> PV (measured ~1850 clocks per 64-key step per CTA).
 // D = 256: S 128 + O 256 columns and 192 KB of Q / K / V tiles leave room for one CTA per SM only.
+// A CTA's register pool is threads x launch registers, and the softmax warpgroup's setmaxnreg.inc is only ever
+// granted if softmax + other <= 2 x launch.
 template <int D>
 struct FwdShape {
   static constexpr int kKeys = (D <= 128) ? 64 : 128;      // keys per tile
