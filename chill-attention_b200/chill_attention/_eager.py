@@ -60,7 +60,7 @@ def _cache():
 
 def _pack(q, k, v):
     """See chill._tensor_core_operands: 16-bit operands TMA cannot describe are packed once."""
-    if q.dtype == torch.float32 or q.shape[-1] not in (64, 128):
+    if q.dtype == torch.float32 or q.shape[-1] not in (64, 128, 256):
         return q, k, v
     ok = _cabi.tma_compatible
     if ok(q) and ok(k) and ok(v):

@@ -57,7 +57,7 @@ def _tensor_core_operands(q, k, v):
     (channel stride != 1, a broadcast dimension, rows not 16-byte aligned): one packing copy each puts them on the
     tensor-core path, ~1000x faster than the generic kernels that would otherwise take the call.  The reference reads
     such tensors through block pointers at full speed (chill_fwd.py:74-98); results are identical either way."""
-    if q.dtype == torch.float32 or q.shape[-1] not in (64, 128):
+    if q.dtype == torch.float32 or q.shape[-1] not in (64, 128, 256):
         return q, k, v
     return tuple(t if _cabi.tma_compatible(t) else t.contiguous() for t in (q, k, v))
 

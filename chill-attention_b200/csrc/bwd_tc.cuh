@@ -35,6 +35,7 @@ constexpr int kBwdThreads = 320;
 constexpr int kBwdComputeThreads = 256;
 constexpr int kTmemColsBwd = 512;
 constexpr bool kHaveBwdTc = true;
+constexpr int kWideCols = 64;  // head dim 256 (bwd_wide.cuh): positions of the streamed axis per step = rows of its TMA boxes
 
 struct BwdTcParams {
   Geo g;

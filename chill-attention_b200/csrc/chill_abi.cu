@@ -292,6 +292,19 @@ static bool bwd_tc_eligible(const chill_bwd_args& a) {
          tma_ok(a.dv, a.dv_strides, s.B, s.H_kv, s.Lk, es) && a.lse_strides[2] == 1;
 }
 
+// 16-bit head dim 256: three tensor-core launches (bwd_wide.cuh); no partial outputs, no per-kernel selection
+static bool bwd_wide_eligible(const chill_bwd_args& a) {
+  const chill_shape& s = a.s;
+  if (!shape_tc_fwd_only_ok(s)) return false;
+  if (a.dk_part != nullptr || a.dv_part != nullptr) return false;
+  if (s.flags & (CHILL_FLAG_BWD_ONLY_DKDV | CHILL_FLAG_BWD_ONLY_DQ)) return false;
+  const size_t es = esize(s.dtype);
+  return tma_ok(a.q, a.q_strides, s.B, s.H, s.Lq, es) && tma_ok(a.k, a.k_strides, s.B, s.H_kv, s.Lk, es) &&
+         tma_ok(a.v, a.v_strides, s.B, s.H_kv, s.Lk, es) && tma_ok(a.d_o, a.do_strides, s.B, s.H, s.Lq, es) &&
+         tma_ok(a.dq, a.dq_strides, s.B, s.H, s.Lq, es) && tma_ok(a.dk, a.dk_strides, s.B, s.H_kv, s.Lk, es) &&
+         tma_ok(a.dv, a.dv_strides, s.B, s.H_kv, s.Lk, es) && a.lse_strides[2] == 1;
+}
+
 static PartOut to_part(const chill_bwd_args& a) {
   PartOut o;
   if (a.dk_part != nullptr && a.dv_part != nullptr && a.part_head + a.part_tail > 0) {
@@ -498,6 +511,31 @@ static int bwd_tc(const chill_bwd_args& a, cudaStream_t st, bool concurrent = tr
   return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_tc launch");
 }
 
+static int bwd_wide(const chill_bwd_args& a, cudaStream_t st) {
+  const chill_shape& s = a.s;
+  CUtensorMap maps[11];
+  const void* in[4] = {a.q, a.k, a.v, a.d_o};
+  const int64_t* in_st[4] = {a.q_strides, a.k_strides, a.v_strides, a.do_strides};
+  const bool in_kv[4] = {false, true, true, false};
+  int rc;
+  for (int i = 0; i < 4; ++i) {
+    const int H = in_kv[i] ? s.H_kv : s.H, L = in_kv[i] ? s.Lk : s.Lq;
+    if ((rc = make_map(&maps[i], in[i], in_st[i], s.B, H, L, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+    if ((rc = make_map(&maps[4 + i], in[i], in_st[i], s.B, H, L, s.D, s.dtype, tc::kWideCols)) != CHILL_OK) return rc;
+  }
+  if ((rc = make_map(&maps[8], a.dq, a.dq_strides, s.B, s.H, s.Lq, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+  if ((rc = make_map(&maps[9], a.dk, a.dk_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+  if ((rc = make_map(&maps[10], a.dv, a.dv_strides, s.B, s.H_kv, s.Lk, s.D, s.dtype, tc::kTile)) != CHILL_OK) return rc;
+  tc::BwdTcParams p;
+  fill_bwd_tc_params(a, p);
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return cuda_fail(cudaGetLastError(), "status symbol");
+  int e = 0;
+  CHILL_MASK_SWITCH(s.mask.id, (e = tc_launch_bwd_wide<MaskT>(s.dtype, maps, p, st)))
+  if (e == 0) g_launches += 3;
+  return e == 0 ? CHILL_OK : cuda_fail((cudaError_t)e, "bwd_wide launch");
+}
+
 // ------------------------------------------------------------- backward without a scratch argument
 // Library-owned scratch for chill_bwd_noalloc: lives in the device image of this file, one copy per
 // GPU that loads the library.  In host code the name below is only a handle for the runtime; the
@@ -591,7 +629,7 @@ int chill_fwd_uses_tensor_cores(const chill_fwd_args* a) {
 int chill_bwd_uses_tensor_cores(const chill_bwd_args* a) {
   int st = check_bwd(a, true);
   if (st != CHILL_OK) return st;
-  return (bwd_tc_eligible(*a) || bwd_tf32_eligible(*a)) ? 1 : 0;
+  return (bwd_tc_eligible(*a) || bwd_wide_eligible(*a) || bwd_tf32_eligible(*a)) ? 1 : 0;
 }
 
 int chill_fwd(const chill_fwd_args* a, void* stream) {
@@ -623,6 +661,7 @@ int chill_bwd(const chill_bwd_args* a, void* stream) {
   int st = check_bwd(a, true);
   if (st != CHILL_OK) return st;
   if (bwd_tc_eligible(*a)) return bwd_tc(*a, (cudaStream_t)stream);
+  if (bwd_wide_eligible(*a)) return bwd_wide(*a, (cudaStream_t)stream);
   if (bwd_tf32_eligible(*a)) return bwd_tf32(*a, (cudaStream_t)stream);
   if (a->s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
   return bwd_generic(*a, (cudaStream_t)stream);
@@ -647,6 +686,7 @@ int chill_bwd_noalloc(const chill_bwd_args* a, void* stream) {
   st = delta_launch(b, (cudaStream_t)stream);
   if (st != CHILL_OK) return st;
   if (bwd_tc_eligible(b)) return bwd_tc(b, (cudaStream_t)stream, /*concurrent=*/false, /*fused=*/false);  // one stream, no helper objects
+  if (bwd_wide_eligible(b)) return bwd_wide(b, (cudaStream_t)stream);
   if (bwd_tf32_eligible(b)) return bwd_tf32(b, (cudaStream_t)stream);
   if (b.s.flags & CHILL_FLAG_REQUIRE_TC) return CHILL_E_UNSUPPORTED;
   return bwd_generic(b, (cudaStream_t)stream);

@@ -3,6 +3,7 @@
 #include "bwd_fused.cuh"
 #include "bwd_tc.cuh"
 #include "bwd_tf32.cuh"
+#include "bwd_wide.cuh"
 #include "fwd_tc.cuh"
 #include "fwd_tf32.cuh"
 #include "tc_launch.h"
@@ -71,6 +72,11 @@ template <>
 int tc_launch_bwd<InstMask>(int dtype, int D, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st) {
   if (p.dq_accum != nullptr) return tc::launch_bwd_fused_all<InstMask>(dtype, D, maps, p, st);
   return tc::launch_bwd_all<InstMask>(dtype, D, maps, p, st);
+}
+
+template <>
+int tc_launch_bwd_wide<InstMask>(int dtype, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st) {
+  return tc::launch_bwd_wide_all<InstMask>(dtype, maps, p, st);
 }
 
 }  // namespace chill

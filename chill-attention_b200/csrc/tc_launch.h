@@ -52,6 +52,11 @@ int tc_launch_fwd_tf32(int D, const CUtensorMap* maps, const tc::FwdTcParams& p,
 template <class M>
 int tc_launch_bwd(int dtype, int D, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st);
 
+// 16-bit head dim 256 (bwd_wide.cuh, three launches); maps: Q, K, V, dO with 128-row boxes, the same four with 64-row
+// boxes, dQ, dK, dV.
+template <class M>
+int tc_launch_bwd_wide(int dtype, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st);
+
 // fp32 tensors in TF32, head dim 64 / 128 (bwd_tf32.cuh, which lists the eleven maps).
 template <class M>
 int tc_launch_bwd_tf32(int D, const CUtensorMap* maps, const tc::BwdTcParams& p, cudaStream_t st);
