@@ -23,9 +23,10 @@
  *
  * Tensors are indexed [batch][head][position][channel]; `*_strides[4]` are in
  * ELEMENTS.  The tensor-core path needs channel stride 1 and 16-byte aligned
- * base / batch / head / position strides for a 16-bit dtype with D in {64,128};
- * anything else (fp32, other D, odd strides) is served by the generic
- * kernels of the same library - there is no host fallback.
+ * base / batch / head / position strides for a 16-bit dtype with D in {64,128,256}
+ * (or fp32 with CHILL_FLAG_ALLOW_TF32 and D in {64,128}); anything else (fp32 in
+ * IEEE arithmetic, other D, odd strides) is served by the generic kernels of the
+ * same library - there is no host fallback.
  *
  * Reference counterparts (alexdremov/chill-attention, paths inside that project):
  *   chill_fwd            replaces the launch of _chill_attn_fwd

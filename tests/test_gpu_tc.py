@@ -60,21 +60,51 @@ def test_dispatch_takes_the_tensor_core_path(_lib):
     q16 = torch.zeros(1, 2, 256, 16, dtype=torch.bfloat16, device="cuda")
     assert uses_tc(_lib, q16, q16, q16, ca.CausalChillMask()) == 0
     q256 = torch.zeros(1, 2, 256, 256, dtype=torch.float16, device="cuda")
-    assert uses_tc(_lib, q256, q256, q256, ca.CausalChillMask()) == 1  # forward only: one CTA per SM
+    assert uses_tc(_lib, q256, q256, q256, ca.CausalChillMask()) == 1  # one CTA per SM
 
 
 @pytest.mark.parametrize("mask", big_masks(), ids=str)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
 @pytest.mark.parametrize("L", [128, 700])
-def test_forward_head_dim_256_on_the_tensor_cores(mask, dtype, L, _lib):
-    """Head dim 256: the forward runs the tcgen05 kernel (S 128 + O 256 TMEM columns, one CTA per SM); the backward
-    of this shape is served by the generic kernels and is covered in test_gpu_generic.py."""
+def test_head_dim_256_on_the_tensor_cores(mask, dtype, L, _lib):
+    """Head dim 256: the forward runs the tcgen05 kernel with S 128 + O 256 TMEM columns (one CTA per SM), the backward
+    three launches of the score-and-accumulate kernel of bwd_wide.cuh (dV, dK, dQ).  GQA, per-row lengths with a row
+    that ends inside a tile, a sequence that is not a multiple of the tile."""
+    from chill_attention.chill import backward_path_counts
+
     q, k, v, do = make_inputs(2, 4, 2, L, 256, dtype, seed=79)
     lens = torch.tensor([L, max(1, L // 3)], dtype=torch.int32)
     assert uses_tc(_lib, q.cuda(), k.cuda(), v.cuda(), mask) == 1
-    o_ref, lse_ref, *_ = oracle_all(mask, q, k, v, do, lens)
-    o, lse, _ = run(mask, q, k, v, do, lens, backward=False)
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do, lens)
+    before = backward_path_counts()
+    o, lse, grads = run(mask, q, k, v, do, lens)
+    after = backward_path_counts()
+    assert after["tensor_core"] == before["tensor_core"] + 1 and after["generic"] == before["generic"]
     check_forward(o, lse, o_ref, lse_ref, lens, dtype)
+    check_grads(grads, g_ref, dtype, lens)
+
+
+def test_head_dim_256_backward_is_reproducible_and_packs_strided_inputs():
+    """No atomics in the head-dim-256 backward: two runs agree bit for bit; operands TMA cannot describe (a
+    transposed view) are packed once and still take the tensor-core kernels."""
+    import chill_attention as ca
+    from chill_attention.chill import backward_path_counts
+
+    mask = ca.SlidingWindowChillMask(150, 20)
+    q, k, v, do = make_inputs(1, 4, 4, 520, 256, torch.bfloat16, seed=80)
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
+    a = run(mask, q, k, v, do)
+    b = run(mask, q, k, v, do)
+    for x, y in zip(a[2], b[2]):
+        assert torch.equal(x, y)
+    # [B, L, H, D] storage viewed as [B, H, L, D]: position-major, which TMA can describe; [B, H, D, L] cannot
+    qd, kd, vd = (t.cuda().transpose(2, 3).contiguous().transpose(2, 3).requires_grad_(True) for t in (q, k, v))
+    before = backward_path_counts()
+    o = ca.chill_attention(qd, kd, vd, mask=mask)
+    o.backward(do.cuda())
+    after = backward_path_counts()
+    assert after["tensor_core"] == before["tensor_core"] + 1
+    check_grads((qd.grad, kd.grad, vd.grad), g_ref, torch.bfloat16)
 
 
 @pytest.mark.parametrize("mask", big_masks(), ids=str)
