@@ -9,8 +9,8 @@
 //   kWideDQ  one CTA per (batch, head, 128 queries):   S = Q K^T,   dP = dO V^T,     W = P (dP - delta),     dQ += W K
 //
 // with P = 2^(S c - LSE) from the stored LSE (no running maximum).  The "row" operands (K / V, resp. Q / dO: 64 KB each)
-// stay in shared memory, the other axis streams through in tiles of 64 positions (one stage: 2 x 32 KB), clipped
-// by the mask functor's range function.  Roles as in fwd_tc.cuh: warps 0-3 own one tile row each per thread and
+// stay in shared memory, the other axis streams through in tiles of 64 positions (one stage: 2 x 32 KB; the tile that
+// only a score GEMM reads is refilled while the step is still running), clipped by the mask functor's range function.  Roles as in fwd_tc.cuh: warps 0-3 own one tile row each per thread and
 // turn the fp32 scores in TMEM into the 16-bit W (written over the scores, A operand of the accumulating GEMM),
 // warp 4 is the TMA producer, warp 5 owns TMEM and issues the MMAs.
 // TMEM columns: [0,64) S (W over its first 32), [64,128) dP, [128,384) accumulator.
@@ -35,7 +35,7 @@ struct WideSmem {
   static constexpr int kC2 = kC1 + kColBytes;
   static constexpr int kVec = kC2 + kColBytes;         // per warp: -LSE and -delta of the 64 streamed columns
   static constexpr int kBars = kVec + 4 * 2 * kWideCols * 4;
-  static constexpr int kNumBars = 6;
+  static constexpr int kNumBars = 8;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;
@@ -105,8 +105,14 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
   const uint32_t sR1 = base + L::kR1, sR2 = base + L::kR2, sC1 = base + L::kC1, sC2 = base + L::kC2;
   float* vec_s = reinterpret_cast<float*>(gen_base + L::kVec);  // [warp][0: -lse, 1: -delta][64]
   const uint32_t bars = base + L::kBars;
-  const uint32_t bar_r_full = bars, bar_c_full = bars + 8, bar_c_empty = bars + 16, bar_t_full = bars + 24,
-                 bar_w_full = bars + 32, bar_acc_full = bars + 40;
+  // The two streamed tiles have different lifetimes: the "early" one (Q for dV, dO / V for dK / dQ) is only read by
+  // a score GEMM and can be refilled while the step is still running; the "late" one is the B operand of the
+  // accumulating GEMM.  e_done = the early tile's GEMM has finished (for dV that is also "scores ready").
+  const uint32_t bar_r_full = bars, bar_ce_full = bars + 8, bar_cl_full = bars + 16, bar_e_done = bars + 24,
+                 bar_cl_empty = bars + 32, bar_t_full = bars + 40, bar_w_full = bars + 48, bar_acc_full = bars + 56;
+  const uint32_t sEarly = MODE == kWideDV ? sC1 : sC2, sLate = MODE == kWideDV ? sC2 : sC1;
+  const CUtensorMap* tmEarly = MODE == kWideDV ? &tmC1 : &tmC2;
+  const CUtensorMap* tmLate = MODE == kWideDV ? &tmC2 : &tmC1;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + L::kMisc + 4);
   const Guard guard{p.status, abort_flag};
@@ -118,8 +124,10 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     if (lane == 0) {
       *abort_flag = 0;
       mbar_init(bar_r_full, 1);
-      mbar_init(bar_c_full, 1);
-      mbar_init(bar_c_empty, 1);
+      mbar_init(bar_ce_full, 1);
+      mbar_init(bar_cl_full, 1);
+      mbar_init(bar_e_done, 1);
+      mbar_init(bar_cl_empty, 1);
       mbar_init(bar_t_full, 1);
       mbar_init(bar_w_full, 4);
       mbar_init(bar_acc_full, 1);
@@ -130,11 +138,12 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         tma_load_4d(sR1 + c * kChunkBytes, &tmR1, bar_r_full, c * 64, rb, hr, b);
         if (kTwoScores) tma_load_4d(sR2 + c * kChunkBytes, &tmR2, bar_r_full, c * 64, rb, hr, b);
       }
-      mbar_arrive_expect_tx(bar_c_full, 2 * L::kColBytes);
-      for (int c = 0; c < kChunks; ++c) {
-        tma_load_4d(sC1 + c * kColChunkBytes, &tmC1, bar_c_full, c * 64, col_pos(0), col_head(0), b);
-        tma_load_4d(sC2 + c * kColChunkBytes, &tmC2, bar_c_full, c * 64, col_pos(0), col_head(0), b);
-      }
+      mbar_arrive_expect_tx(bar_ce_full, L::kColBytes);
+      for (int c = 0; c < kChunks; ++c)
+        tma_load_4d(sEarly + c * kColChunkBytes, tmEarly, bar_ce_full, c * 64, col_pos(0), col_head(0), b);
+      mbar_arrive_expect_tx(bar_cl_full, L::kColBytes);
+      for (int c = 0; c < kChunks; ++c)
+        tma_load_4d(sLate + c * kColChunkBytes, tmLate, bar_cl_full, c * 64, col_pos(0), col_head(0), b);
     }
   } else if (warp == 5) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -152,13 +161,17 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     if (lane == 0) {
       bool ok = true;
       for (int it = 1; it < n_it && ok; ++it) {  // tile 0 was issued during set-up
-        ok = mbar_wait(bar_c_empty, (uint32_t)(it - 1) & 1u, guard, kStWideProducer);
+        const uint32_t prev = (uint32_t)(it - 1) & 1u;
+        ok = mbar_wait(bar_e_done, prev, guard, kStWideProducer);
         if (!ok) break;
-        mbar_arrive_expect_tx(bar_c_full, 2 * L::kColBytes);
-        for (int c = 0; c < kChunks; ++c) {
-          tma_load_4d(sC1 + c * kColChunkBytes, &tmC1, bar_c_full, c * 64, col_pos(it), col_head(it), b);
-          tma_load_4d(sC2 + c * kColChunkBytes, &tmC2, bar_c_full, c * 64, col_pos(it), col_head(it), b);
-        }
+        mbar_arrive_expect_tx(bar_ce_full, L::kColBytes);
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_4d(sEarly + c * kColChunkBytes, tmEarly, bar_ce_full, c * 64, col_pos(it), col_head(it), b);
+        ok = mbar_wait(bar_cl_empty, prev, guard, kStWideProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_cl_full, L::kColBytes);
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_4d(sLate + c * kColChunkBytes, tmLate, bar_cl_full, c * 64, col_pos(it), col_head(it), b);
       }
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
@@ -177,23 +190,28 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       // the streamed tile that multiplies W: dO for dV, Q for dK, K for dQ; MN-major, channel blocks one chunk apart
       const uint32_t x_lo = desc_lo_sw128(MODE == kWideDV ? sC2 : sC1, kColChunkBytes);
       bool ok = mbar_wait(bar_r_full, 0, guard, kStWideMma);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const uint32_t par = (uint32_t)it & 1u;
-        ok = mbar_wait(bar_c_full, par, guard, kStWideMma);
-        if (!ok) break;
-        tc_fence_after();
-        // scores: rows x 64 streamed positions, contraction over the D channels (both operands K-major)
+      auto score = [&](uint32_t t_dst, uint32_t r_lo, uint32_t c_lo) {  // rows x 64 positions, contraction over D
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss_lh(tS, r1_lo + kmajor_step(kk), c1_lo + (uint32_t)((kk / 4) * (kColChunkBytes / 16) + (kk % 4) * 2), hi_k,
+          mma_ss_lh(t_dst, r_lo + kmajor_step(kk), c_lo + (uint32_t)((kk / 4) * (kColChunkBytes / 16) + (kk % 4) * 2), hi_k,
                     idesc_s, kk > 0 ? 1u : 0u);
+      };
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint32_t par = (uint32_t)it & 1u;
+        // the GEMM that reads the early tile: S for dV, dP for dK / dQ
+        ok = mbar_wait(bar_ce_full, par, guard, kStWideMma);
+        if (!ok) break;
+        tc_fence_after();
+        if (MODE == kWideDV) score(tS, r1_lo, c1_lo);
+        else score(tdP, r2_lo, c2_lo);
+        mma_commit(bar_e_done);
+        ok = mbar_wait(bar_cl_full, par, guard, kStWideMma);
+        if (!ok) break;
+        tc_fence_after();
         if (kTwoScores) {
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk)
-            mma_ss_lh(tdP, r2_lo + kmajor_step(kk), c2_lo + (uint32_t)((kk / 4) * (kColChunkBytes / 16) + (kk % 4) * 2), hi_k,
-                      idesc_s, kk > 0 ? 1u : 0u);
+          score(tS, r1_lo, c1_lo);
+          mma_commit(bar_t_full);
         }
-        mma_commit(bar_t_full);
         ok = mbar_wait(bar_w_full, par, guard, kStWideMma);
         if (!ok) break;
         tc_fence_after();
@@ -201,7 +219,7 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < CT / 16; ++kk)
           mma_ts_lh(tAcc, tS + kk * 8, x_lo + kk * 128, hi_k, idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(bar_c_empty);  // the streamed tiles (and S / dP) may be overwritten
+        mma_commit(bar_cl_empty);  // the late tile, S and dP may be overwritten
       }
       if (ok) mma_commit(bar_acc_full);
     }
@@ -242,7 +260,7 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         }
         __syncwarp();
       }
-      ok = mbar_wait(bar_t_full, par, guard, kStWideCompute);
+      ok = mbar_wait(kTwoScores ? bar_t_full : bar_e_done, par, guard, kStWideCompute);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
