@@ -4,7 +4,7 @@ import ctypes
 import pytest
 import torch
 
-from helpers import all_masks, big_masks, check_forward, check_grads, ensure_built, make_inputs, oracle_all
+from helpers import O_ATOL, all_masks, big_masks, check_forward, check_grads, ensure_built, make_inputs, oracle_all
 
 pytestmark = pytest.mark.gpu
 
@@ -213,6 +213,7 @@ def test_host_buffer_pipeline_matches_device_path():
     q, k, v, do = make_inputs(5, 4, 2, 384, 128, torch.bfloat16)
     host = [t.pin_memory() for t in (q, k, v, do)]
     ca.set_deterministic(True)  # two-kernel backward: chunking must not change a single bit
+    o_ref, lse_ref, *g_ref = oracle_all(mask, q, k, v, do)
     try:
         o, lse, grads = run(mask, q, k, v, do)
         for chunk, heads in ((1, None), (2, 4), (8, 4), (1, 2)):
@@ -220,6 +221,9 @@ def test_host_buffer_pipeline_matches_device_path():
             assert torch.equal(oh, o.detach().cpu())
             for a, b in zip((dqh, dkh, dvh), grads):
                 assert torch.equal(a, b.cpu())
+        # and against the oracle directly, not only against the device-resident path
+        assert (oh.double() - o_ref).abs().max() <= O_ATOL[torch.bfloat16]
+        check_grads((dqh, dkh, dvh), g_ref, torch.bfloat16)
     finally:
         ca.set_deterministic(False)
     # default (single-kernel backward, dQ summed with fp32 reductions): equal up to the order of those sums
