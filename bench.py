@@ -84,6 +84,9 @@ WORKLOADS = {
     # fp32 tensors with precision="tf32": forward and backward on the TF32 tensor cores (two-kernel backward)
     "c2f32": ("CausalChillMask", (), "float32", 2, 16, 4096, 128),
     "c2f32d64": ("CausalChillMask", (), "float32", 2, 32, 4096, 64),
+    # head dim 256: tensor-core forward (one CTA per SM) and the three-launch backward; "s" = a quarter of the batch
+    "c2d256": ("CausalChillMask", (), "bfloat16", 8, 16, 4096, 256),
+    "c2d256s": ("CausalChillMask", (), "bfloat16", 2, 16, 4096, 256),
 }
 
 
@@ -357,8 +360,10 @@ def run_ours(args):
     def run_dq():
         _cabi.check(lib, lib.chill_bwd(C.byref(bargs_dq), stream), "chill_bwd(dq)")
 
-    if dq_accum is not None:
+    wide = D == 256 and dtype in (torch.float16, torch.bfloat16)  # three launches behind one chill_bwd call
+    if dq_accum is not None or wide:
         # "bwd" = zero-fill of the scratch + the fused kernel + the fp32 -> 16-bit conversion of dQ
+        # (head dim 256: the dV, dK and dQ launches)
         parts = (("fwd", run_fwd), ("delta", run_delta), ("bwd", run_bwd))
         kflops = {"fwd": 4.0, "bwd": 10.0}
     else:
@@ -526,8 +531,9 @@ def run_ours(args):
                 "l2": "inputs+outputs per step and GPU (%.0f MB) exceed the 126 MB L2; no explicit flush"
                       % (8 * units_max * L * D * esz / 1e6),
                 "tensor_core_path": bool(uses_tc == 1),
-                "backward": "single kernel, 5 GEMMs per tile pair, dQ summed in fp32 scratch" if args.bwd == "fused"
-                            else "two kernels (dK/dV, dQ), 7 GEMMs per tile pair, bitwise reproducible"},
+                "backward": ("three launches (dV, dK, dQ), 8 GEMMs per tile pair, bitwise reproducible" if wide
+                             else "single kernel, 5 GEMMs per tile pair, dQ summed in fp32 scratch" if args.bwd == "fused"
+                             else "two kernels (dK/dV, dQ), 7 GEMMs per tile pair, bitwise reproducible")},
             "fwd": {"tflops": round(fwd_tflops, 2), "ms": round(fwd_ms, 4),
                     "pct_of_measured_peak": round(100 * fwd_tflops / world / peak, 2),
                     "pct_of_nominal_peak": round(100 * fwd_tflops / world / NOMINAL_BF16_TFLOPS, 2)},
