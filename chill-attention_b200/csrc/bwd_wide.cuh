@@ -96,6 +96,7 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
   const long long o_sl = MODE == kWideDV ? p.dv_sl : (MODE == kWideDK ? p.dk_sl : p.dq_sl);
   if (n_it == 0) {  // padding rows, or rows nothing on this shard can see: zero gradient
     zero_rows<T, D>(out_base + b * o_sb + hr * o_sh + rb * o_sl, o_sl, rows_here, kWideThreads);
+    if (MODE == kWideDV) zero_part_rows<D>(p.part, b, hr, rb, rows_here, g.Lk, kWideThreads);  // dK and dV partials
     return;
   }
 
@@ -300,6 +301,8 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     const float mul = MODE == kWideDV ? 1.f : g.scale;
+    // optional un-rounded fp32 copy of this key row's dV / dK (first / last key rows of the call, see PartOut)
+    float* part_row = kKeyRows ? p.part.row(MODE == kWideDV ? p.part.dv : p.part.dk, b, hr, rb + r, g.Lk) : nullptr;
 #pragma unroll 1
     for (int q4 = 0; q4 < D / 32; ++q4) {
       uint32_t acc[32];
@@ -308,6 +311,7 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
         tmem_wait_ld();
       }
       stage_row32<T>(gen_base + L::kR1, r, q4, acc, mul, ok && row_ok);
+      if (part_row != nullptr) store_part32(part_row + q4 * 32, acc, mul, ok && row_ok);
     }
     fence_proxy_async_smem();
     named_bar_sync(1, 128);

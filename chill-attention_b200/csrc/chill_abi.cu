@@ -292,11 +292,10 @@ static bool bwd_tc_eligible(const chill_bwd_args& a) {
          tma_ok(a.dv, a.dv_strides, s.B, s.H_kv, s.Lk, es) && a.lse_strides[2] == 1;
 }
 
-// 16-bit head dim 256: three tensor-core launches (bwd_wide.cuh); no partial outputs, no per-kernel selection
+// 16-bit head dim 256: three tensor-core launches (bwd_wide.cuh); no per-kernel selection
 static bool bwd_wide_eligible(const chill_bwd_args& a) {
   const chill_shape& s = a.s;
   if (!shape_tc_fwd_only_ok(s)) return false;
-  if (a.dk_part != nullptr || a.dv_part != nullptr) return false;
   if (s.flags & (CHILL_FLAG_BWD_ONLY_DKDV | CHILL_FLAG_BWD_ONLY_DQ)) return false;
   const size_t es = esize(s.dtype);
   return tma_ok(a.q, a.q_strides, s.B, s.H, s.Lq, es) && tma_ok(a.k, a.k_strides, s.B, s.H_kv, s.Lk, es) &&

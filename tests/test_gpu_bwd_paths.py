@@ -173,7 +173,7 @@ def test_misaligned_dq_scratch_is_rejected(lib):
     torch.cuda.synchronize()
 
 
-@pytest.mark.parametrize("form", ["single_kernel", "two_kernel", "generic"])
+@pytest.mark.parametrize("form", ["single_kernel", "two_kernel", "generic", "head_dim_256"])
 @pytest.mark.parametrize("layout", ["rows_major", "heads_major"])
 def test_fp32_partial_copies_of_dk_dv(lib, form, layout):
     """chill_bwd_args.dk_part / dv_part: un-rounded fp32 dK / dV of the first `head` and last `tail` key rows.
@@ -185,7 +185,7 @@ def test_fp32_partial_copies_of_dk_dv(lib, form, layout):
     from chill_attention import _cabi
 
     mask = ca.SlidingWindowChillMask(300, 40)
-    B, H, Hkv, L, D, dtype = 2, 4, 2, 700, 128, torch.bfloat16
+    B, H, Hkv, L, D, dtype = 2, 4, 2, 700, (256 if form == "head_dim_256" else 128), torch.bfloat16
     q, k, v, do = make_inputs(B, H, Hkv, L, D, dtype, seed=36)
     lens = torch.tensor([L, 650], dtype=torch.int32)  # the last key tile of batch row 1 is partly padding
     _, _, _, dk_ref, dv_ref = oracle_all(mask, q, k, v, do, lens)
