@@ -60,7 +60,7 @@ def test_custom_library_builds_and_exports(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float32, 32)], ids=str)
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float32, 32), (torch.float16, 256), (torch.bfloat16, 32)], ids=str)
 def test_custom_mask_on_gpu(dtype, D):
     from chill_attention import chill_attention
     from oracle import attention_oracle as orc
