@@ -75,9 +75,15 @@ def test_noalloc_matches_regular_backward_twice_in_a_row():
     for a, b in zip(out3, out1):
         assert torch.equal(a, b)
     assert lib.chill_read_device_status() == 0
+    # call 4: head dim 256 (the three-launch tensor-core backward; bitwise reproducible, so equal to the regular path)
+    p4 = _problem(lib, ca.PrefixLMChillMask(100), 1, 4, 2, 520, 256, torch.float16, seed=7)
+    out4, ref4 = _both_paths(lib, p4)
+    for a, b in zip(out4, ref4):
+        assert torch.equal(a, b)
     # not only equal to the regular path: right, against the fp64 dense-mask oracle
     for prob, out, mask, dtype, ln in ((p1, out1, ca.CausalChillMask(), torch.bfloat16, None),
-                                       (p2, out2, ca.SlidingWindowChillMask(40, 3), torch.float32, lens)):
+                                       (p2, out2, ca.SlidingWindowChillMask(40, 3), torch.float32, lens),
+                                       (p4, out4, ca.PrefixLMChillMask(100), torch.float16, None)):
         q, k, v, do = (t.cpu() for t in prob[:4])
         check_grads(out, oracle_all(mask, q, k, v, do, ln)[2:], dtype, ln)
 
