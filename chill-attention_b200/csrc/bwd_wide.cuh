@@ -8,11 +8,12 @@
 //   kWideDK  same rows:                                S^T = K Q^T, dP^T = V dO^T,   W = P^T (dP^T - delta), dK += W Q
 //   kWideDQ  one CTA per (batch, head, 128 queries):   S = Q K^T,   dP = dO V^T,     W = P (dP - delta),     dQ += W K
 //
-// with P = 2^(S c - LSE) from the stored LSE (no running maximum).  The "row" operands (K / V, resp. Q / dO: 64 KB each)
-// stay in shared memory, the other axis streams through in tiles of 64 positions (one stage: 2 x 32 KB; the tile that
-// only a score GEMM reads is refilled while the step is still running), clipped by the mask functor's range function.  Roles as in fwd_tc.cuh: warps 0-3 own one tile row each per thread and
-// turn the fp32 scores in TMEM into the 16-bit W (written over the scores, A operand of the accumulating GEMM),
-// warp 4 is the TMA producer, warp 5 owns TMEM and issues the MMAs.
+// with P = 2^(S c - LSE) from the stored LSE (no running maximum).  The "row" operands (K / V, resp. Q / dO: 64 KB
+// each) stay in shared memory, the other axis streams through in tiles of 64 positions (one stage: 2 x 32 KB; the
+// tile that only a score GEMM reads is refilled while the step is still running), clipped by the mask functor's
+// range function.  Roles as in fwd_tc.cuh: warps 0-3 own one tile row each per thread and turn the fp32 scores in
+// TMEM into the 16-bit W (written over the scores, A operand of the accumulating GEMM), warp 4 is the TMA producer,
+// warp 5 owns TMEM and issues the MMAs.
 // TMEM columns: [0,64) S (W over its first 32), [64,128) dP, [128,384) accumulator.
 // Reference math: chill_attention/chill_bwd_dkdv.py:347-508, chill_bwd_dq.py:300-394.
 #pragma once
