@@ -241,6 +241,13 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       row_nl = (lv == -CUDART_INF_F) ? 0.f : -lv;
       row_nd = -p.delta[((long long)b * g.H + hr) * g.Lq + rb + r];
     }
+    // streamed positions that EVERY row of this tile sees (half-open, global): tiles inside skip the mask arithmetic
+    int full_lo = 0, full_hi = 0;
+    constexpr bool kHasFull = kKeyRows ? M::kHasQFullRange : M::kHasKFullRange;
+    if (kHasFull && rg0 + kTile <= n && rows_here == kTile) {
+      if (kKeyRows) M::q_full_range_for_k(rg0, kTile, n, g.margs, full_lo, full_hi);
+      else M::k_full_range_for_q(rg0, kTile, n, g.margs, full_lo, full_hi);
+    }
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const uint32_t par = (uint32_t)it & 1u;
@@ -266,30 +273,38 @@ bwd_wide_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM accesses
       if (!ok) break;
       tc_fence_after();
+      const bool full = kHasFull && cg0 >= full_lo && cg0 + CT <= full_hi && clim >= CT;
       uint32_t w[CT / 2];
+      auto body = [&](auto masked_tag) {  // two copies: full tiles run without any mask arithmetic
+        constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {  // 32 streamed positions at a time
-        uint32_t sreg[32], dreg[32];
-        tmem_ld32(tS + lane_sel + half * 32, sreg);
-        if (kTwoScores) tmem_ld32(tdP + lane_sel + half * 32, dreg);
-        tmem_wait_ld();
+        for (int half = 0; half < 2; ++half) {  // 32 streamed positions at a time
+          uint32_t sreg[32], dreg[32];
+          tmem_ld32(tS + lane_sel + half * 32, sreg);
+          if (kTwoScores) tmem_ld32(tdP + lane_sel + half * 32, dreg);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float wv[2];
+          for (int i = 0; i < 32; i += 2) {
+            float wv[2];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int cc = half * 32 + i + e;
-            const float nl = kKeyRows ? vb[cc] : row_nl;
-            const float nd = kKeyRows ? vb[CT + cc] : row_nd;
-            const int qg = kKeyRows ? cg0 + cc : rg, kg = kKeyRows ? rg : cg0 + cc;
-            const bool vis = row_ok && cc < clim && M::mask(qg, kg, n, g.margs);
-            float pv = vis ? ex2(fmaf(__uint_as_float(sreg[i + e]), c, nl)) : 0.f;
-            if (kTwoScores) pv *= __uint_as_float(dreg[i + e]) + nd;
-            wv[e] = pv;
+            for (int e = 0; e < 2; ++e) {
+              const int cc = half * 32 + i + e;
+              const float nl = kKeyRows ? vb[cc] : row_nl;
+              const float nd = kKeyRows ? vb[CT + cc] : row_nd;
+              float pv = ex2(fmaf(__uint_as_float(sreg[i + e]), c, nl));
+              if (kMasked) {
+                const int qg = kKeyRows ? cg0 + cc : rg, kg = kKeyRows ? rg : cg0 + cc;
+                pv = (row_ok && cc < clim && M::mask(qg, kg, n, g.margs)) ? pv : 0.f;
+              }
+              if (kTwoScores) pv *= __uint_as_float(dreg[i + e]) + nd;
+              wv[e] = pv;
+            }
+            w[half * 16 + i / 2] = pack2<T>(wv[0], wv[1]);
           }
-          w[half * 16 + i / 2] = pack2<T>(wv[0], wv[1]);
         }
-      }
+      };
+      if (full) body(std::false_type{});
+      else body(std::true_type{});
       tmem_st32(tS + lane_sel, w);  // CT / 2 = 32 columns of 16-bit pairs over the scores just consumed
       tmem_wait_st();
       tc_fence_before();
